@@ -122,11 +122,13 @@ class CacheGroup:
         # written before any query can see it, but the tensor-core attention fetches whole pages, masked slots
         # included, and a masked probability of 0 times a stray NaN would still be NaN.
         self.k = {c: torch.zeros(shape, dtype=dtype, device=device) for c in owners}
-        self.v = {c: torch.zeros(v_shape, dtype=dtype, device=device) for c in owners}
+        # (where the key rows are the values too, the value pool is the key pool under a second name)
+        self.v = self.k if req.values_in_keys else {c: torch.zeros(v_shape, dtype=dtype, device=device) for c in owners}
 
     def bytes_per_token(self) -> int:
         any_pool = next(iter(self.k.values()))
-        return len(self.owners) * self.req.kv_heads * (self.req.head_dim + self.req.value_dim) * any_pool.element_size()
+        row = self.req.head_dim + (0 if self.req.values_in_keys else self.req.value_dim)
+        return len(self.owners) * self.req.kv_heads * row * any_pool.element_size()
 
 
 @dataclass
@@ -165,8 +167,9 @@ class CacheManager:
                 src = plans[plan.cache_from]
                 if src.kv is None or src.cache_from is not None:
                     raise ValueError(f"call {ci} reads the cache of call {plan.cache_from}, which owns none")
-                if plan.kv is not None and (plan.kv.kv_heads, plan.kv.head_dim, plan.kv.value_dim) != \
-                        (src.kv.kv_heads, src.kv.head_dim, src.kv.value_dim):
+                if plan.kv is not None and (plan.kv.kv_heads, plan.kv.head_dim, plan.kv.value_dim,
+                                            plan.kv.values_in_keys) != \
+                        (src.kv.kv_heads, src.kv.head_dim, src.kv.value_dim, src.kv.values_in_keys):
                     raise ValueError(f"call {ci} and call {plan.cache_from} disagree on the cache geometry")
                 # pages are given back by the owner's window: a reader that looks further back than the owner
                 # would ask for keys whose pages are gone
@@ -283,7 +286,8 @@ class CacheManager:
             index = torch.tensor(ids, dtype=torch.long, device=self.device)
             for c in g.owners:
                 snap.k[c] = g.k[c].index_select(0, index).cpu()
-                snap.v[c] = g.v[c].index_select(0, index).cpu()
+                if not g.req.values_in_keys:
+                    snap.v[c] = g.v[c].index_select(0, index).cpu()
         for c, t in self.state.items():
             snap.state[c] = t[rec.slot].to("cpu", copy=True)
         return snap
@@ -307,7 +311,8 @@ class CacheManager:
                     self.release(request_id)
                     raise PageError("the snapshot does not fit this cache's page size")
                 g.k[c].index_copy_(0, index, snap.k[c].to(self.device))
-                g.v[c].index_copy_(0, index, snap.v[c].to(self.device))
+                if not g.req.values_in_keys:
+                    g.v[c].index_copy_(0, index, snap.v[c].to(self.device))
         for c, t in self.state.items():
             t[slot].copy_(snap.state[c])
         return rec

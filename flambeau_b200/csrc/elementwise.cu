@@ -496,7 +496,8 @@ FB_API int fb_concat_cast(const float* a, const float* b, void* out, int out_dty
 // Formula: crates/kernels-hip/src/kernels/rope_neox_partial_f16.cu:39-46.
 // ---------------------------------------------------------------------------
 __global__ void rope_table_kernel(const int* __restrict__ positions, const double* __restrict__ inv_freq,
-                                  float* __restrict__ cos_t, float* __restrict__ sin_t, int n, int half) {
+                                  float* __restrict__ cos_t, float* __restrict__ sin_t, int n, int half,
+                                  float magnitude) {
     fb_pdl_launch_dependents();
     fb_pdl_wait();
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
@@ -504,16 +505,16 @@ __global__ void rope_table_kernel(const int* __restrict__ positions, const doubl
     const int t = idx / half, i = idx - t * half;
     double s, c;
     sincos((double)positions[t] * inv_freq[i], &s, &c);
-    cos_t[idx] = (float)c;
-    sin_t[idx] = (float)s;
+    cos_t[idx] = (float)c * magnitude;       // (1 in the plain case; a stretch of the frequencies scales both tables)
+    sin_t[idx] = (float)s * magnitude;
 }
 
 FB_API int fb_rope_table(const int* positions, const double* inv_freq, float* cos_t, float* sin_t, int n,
-                         int half, cudaStream_t stream) {
+                         int half, float magnitude, cudaStream_t stream) {
     FB_REQUIRE(n >= 0 && half > 0, "rope_table: bad sizes n=%d half=%d", n, half);
     if (n == 0) return 0;
     const int total = n * half;
-    fb_launch((rope_table_kernel), (total + 255) / 256, 256, 0, stream, positions, inv_freq, cos_t, sin_t, n, half);
+    fb_launch((rope_table_kernel), (total + 255) / 256, 256, 0, stream, positions, inv_freq, cos_t, sin_t, n, half, magnitude);
     return fb_check_launch("rope_table");
 }
 

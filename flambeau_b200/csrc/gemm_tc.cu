@@ -454,16 +454,20 @@ FB_API int fb_gemm_tc(const void* X, long long lda, const void* W, long long ldw
 // The grouped form: out[m] = act(X[m] * W[g]^T) with g = tile_group[m / tile] and W [groups, N, K] contiguous; the M
 // rows come in whole tiles of `tile` (16, 32, 64 or 128) rows, each of one group (negative: skipped, its rows are
 // left as they are).  `act` is an FbPlainAct code.  For the products of routed experts over tokens sorted by expert.
-FB_API int fb_gemm_tc_grouped(const void* X, long long lda, const void* W, long long ldw, int groups,
+static int gemm_tc_grouped(const void* X, long long lda, const void* W, long long ldw, int groups,
                               const int* tile_group, int tile, void* out, int o_dtype, long long ldo, int M, int N,
-                              int K, int act, int* status, cudaStream_t stream) {
+                              int K, int act, int gated, int* status, cudaStream_t stream) {
     FB_REQUIRE(M >= 0 && N > 0 && K > 0 && groups > 0, "gemm_tc_grouped: bad sizes M=%d N=%d K=%d", M, N, K);
     FB_REQUIRE(tile == 16 || tile == 32 || tile == 64 || tile == 128, "gemm_tc_grouped: row tiles of 16 to 128, not %d", tile);
     FB_REQUIRE(M % tile == 0 && tile_group, "gemm_tc_grouped: the rows must be whole tiles with a group each");
-    FB_REQUIRE(lda >= K && ldw >= K && ldo >= N, "gemm_tc_grouped: a row stride is shorter than its row");
+    FB_REQUIRE(lda >= K && ldw >= K, "gemm_tc_grouped: a row stride is shorter than its row");
     FB_REQUIRE(lda % 8 == 0 && ldw % 8 == 0, "gemm_tc_grouped: row strides must be multiples of 8 elements");
     FB_REQUIRE(((uintptr_t)X & 15) == 0 && ((uintptr_t)W & 15) == 0, "gemm_tc_grouped: operands must be 16-byte aligned");
     FB_REQUIRE(fb_plain_act_known(act), "gemm_tc_grouped: unknown activation code %d", act);
+    FB_REQUIRE(!gated || (fb_act_known(gated) && !act && N % 2 == 0), "gemm_tc_grouped: a gate needs a known activation, "
+               "an even number of stacked rows and no plain activation beside it");
+    if (gated) FB_REQUIRE(ldo >= N / 2, "gemm_tc_grouped: a row stride is shorter than its row");
+    else FB_REQUIRE(ldo >= N, "gemm_tc_grouped: a row stride is shorter than its row");
     FB_REQUIRE((long long)groups * N < 2147483647LL, "gemm_tc_grouped: too many weight rows");
     if (M == 0) return 0;
     CUtensorMap mw, mx;
@@ -477,13 +481,13 @@ FB_API int fb_gemm_tc_grouped(const void* X, long long lda, const void* W, long 
             return act ? launch_tc<BN_, float, true>(mw, mx, out, (long)ldo, 0, 1, nullptr, nullptr, 0, nullptr, 0, M, \
                                                      N, K, 1, status, stream, 0, tile_group, N, act)            \
                        : launch_tc<BN_, float>(mw, mx, out, (long)ldo, 0, 1, nullptr, nullptr, 0, nullptr, 0, M, N, K, \
-                                               1, status, stream, 0, tile_group, N, 0);                         \
+                                               1, status, stream, gated, tile_group, N, 0);                         \
         else if (o_dtype == FB_BF16)                                                                            \
             return act ? launch_tc<BN_, __nv_bfloat16, true>(mw, mx, out, (long)ldo, 0, 1, nullptr, nullptr, 0, \
                                                              nullptr, 0, M, N, K, 1, status, stream, 0,         \
                                                              tile_group, N, act)                                \
                        : launch_tc<BN_, __nv_bfloat16>(mw, mx, out, (long)ldo, 0, 1, nullptr, nullptr, 0, nullptr, 0, \
-                                                       M, N, K, 1, status, stream, 0, tile_group, N, 0);        \
+                                                       M, N, K, 1, status, stream, gated, tile_group, N, 0);        \
         break;
     switch (tile) {
         FB_TCGR_CASE(16)
@@ -493,6 +497,21 @@ FB_API int fb_gemm_tc_grouped(const void* X, long long lda, const void* W, long 
     }
 #undef FB_TCGR_CASE
     return fb_fail(-1, "gemm_tc_grouped: unknown output dtype code %d", o_dtype);
+}
+
+FB_API int fb_gemm_tc_grouped(const void* X, long long lda, const void* W, long long ldw, int groups,
+                              const int* tile_group, int tile, void* out, int o_dtype, long long ldo, int M, int N,
+                              int K, int act, int* status, cudaStream_t stream) {
+    return gemm_tc_grouped(X, lda, W, ldw, groups, tile_group, tile, out, o_dtype, ldo, M, N, K, act, 0, status, stream);
+}
+
+// The grouped form of the gated product: W [groups, N, K] stacks every group's gate and up rows alternately and
+// out[m, c] = act(g_c) * u_c with (g_0, u_0, g_1, u_1, ...) = X[m] * W[g]^T, `gated` an FbAct code; out has N / 2 columns.
+FB_API int fb_gemm_tc_grouped_gated(const void* X, long long lda, const void* W, long long ldw, int groups,
+                                    const int* tile_group, int tile, void* out, int o_dtype, long long ldo, int M,
+                                    int N, int K, int gated, int* status, cudaStream_t stream) {
+    FB_REQUIRE(fb_act_known(gated), "gemm_tc_grouped_gated: unknown activation code %d", gated);
+    return gemm_tc_grouped(X, lda, W, ldw, groups, tile_group, tile, out, o_dtype, ldo, M, N, K, 0, gated, status, stream);
 }
 
 // acc[M,N] += X[M,K] * W[N,K]^T in float32 where the product is one that leaves in whole tiles through the two-SM

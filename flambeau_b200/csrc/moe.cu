@@ -4,12 +4,15 @@
 //   moe_choose   per token (one warp): the router's logits (a product of the token rows with the router matrix, summed
 //                in float32) plus the bias, the `top` largest (the lower index wins a tie), their weights = softmax
 //                over the chosen logits only; optionally one more number per token, sigmoid of one more column of
-//                that product (w_gate . h), for a shared expert
+//                that product (w_gate . h), for a shared expert.  A second rule (`rule` 1): scores = softmax of the
+//                logits over all experts, the `top` largest of score + bias are chosen, the weights are the chosen
+//                scores themselves, divided by their sum and multiplied by `weight_scale`
 //   moe_sort     one CTA: (token, choice) pairs counted per expert, every expert's stretch padded to a multiple of
 //                the products' row tile, so that a row tile belongs to one expert; writes for every place of the
 //                padded order its token (-1: padding), for every pair its place, for every row tile its expert
 //                (-1: unused).  Sizes are upper bounds known on the host, so nothing has to come back from the device
-//   moe_combine  per token: sum_k weight_k * expert_out[place of (token, k)] + gate * shared_out
+//   moe_combine  per token: sum_k weight_k * expert_out[place of (token, k)] + gate * shared_out; a chosen expert
+//                beyond the ones that have weights (an identity expert) hands the token's own input on
 #include "common.cuh"
 
 constexpr int MOE_MAX_LOGITS_PER_LANE = 16;            // 512 experts at most
@@ -18,7 +21,7 @@ template <typename TW>
 __global__ void __launch_bounds__(128)
 moe_choose_kernel(const float* __restrict__ z_in, long z_stride, int n_partials, long partial_stride,
                   const TW* __restrict__ br, int gate_col, int n, int E, int K, int* __restrict__ chosen,
-                  float* __restrict__ share, float* __restrict__ gate) {
+                  float* __restrict__ share, float* __restrict__ gate, int rule, float weight_scale) {
     fb_pdl_launch_dependents();
     fb_pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -31,6 +34,57 @@ moe_choose_kernel(const float* __restrict__ z_in, long z_stride, int n_partials,
         return v;
     };
     float z[MOE_MAX_LOGITS_PER_LANE];                  // lane l keeps the logits of experts l, l + 32, ...
+    if (rule == 1) {
+        // scores over all experts first; the bias only moves the choice
+        float s[MOE_MAX_LOGITS_PER_LANE];
+        float top = -INFINITY;
+#pragma unroll
+        for (int r = 0; r < MOE_MAX_LOGITS_PER_LANE; ++r) {
+            const int e = lane + 32 * r;
+            s[r] = e < E ? logit(e) : -INFINITY;
+            top = fmaxf(top, s[r]);
+        }
+        top = fb_warp_max(top);
+        float sum = 0.0f;
+#pragma unroll
+        for (int r = 0; r < MOE_MAX_LOGITS_PER_LANE; ++r) {
+            s[r] = lane + 32 * r < E ? expf(s[r] - top) : 0.0f;
+            sum += s[r];
+        }
+        sum = fb_warp_sum(sum);
+#pragma unroll
+        for (int r = 0; r < MOE_MAX_LOGITS_PER_LANE; ++r) {
+            const int e = lane + 32 * r;
+            s[r] = s[r] / sum;
+            z[r] = e < E ? s[r] + (br ? fb_to_float(br[e]) : 0.0f) : -INFINITY;
+        }
+        float total = 0.0f, mine = 0.0f;               // lane k keeps the k-th chosen score
+        for (int k = 0; k < K; ++k) {
+            float best = -INFINITY, best_s = 0.0f;
+            int best_e = 0x7fffffff;
+#pragma unroll
+            for (int r = 0; r < MOE_MAX_LOGITS_PER_LANE; ++r) {
+                const int e = lane + 32 * r;
+                if (e < E && (z[r] > best)) { best = z[r]; best_e = e; best_s = s[r]; }
+            }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, off);
+                const float os = __shfl_xor_sync(0xffffffffu, best_s, off);
+                const int oe = __shfl_xor_sync(0xffffffffu, best_e, off);
+                if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; best_s = os; }
+            }
+#pragma unroll
+            for (int r = 0; r < MOE_MAX_LOGITS_PER_LANE; ++r)
+                if (best_e == lane + 32 * r) z[r] = -INFINITY;           // taken
+            total += best_s;
+            if (lane == k) mine = best_s;
+            if (lane == 0) chosen[(size_t)row * K + k] = best_e;
+        }
+        if (lane < K) share[(size_t)row * K + lane] = mine / (total + 1e-20f) * weight_scale;
+        if (gate_col >= 0 && lane == 0) gate[row] = 1.0f / (1.0f + expf(-logit(gate_col)));
+        return;
+    }
 #pragma unroll
     for (int r = 0; r < MOE_MAX_LOGITS_PER_LANE; ++r) {
         const int e = lane + 32 * r;
@@ -101,10 +155,12 @@ moe_sort_kernel(const int* __restrict__ chosen, int pairs, int K, int E, int til
     }
 }
 
+template <typename T>
 __global__ void moe_combine_kernel(const float* __restrict__ expert_out, long expert_stride,
                                    const int* __restrict__ pair_place, const float* __restrict__ share, int K,
                                    const float* __restrict__ shared_out, int shared_partials, long shared_partial_stride,
-                                   const float* __restrict__ gate, float* __restrict__ out, int n, int D) {
+                                   const float* __restrict__ gate, float* __restrict__ out, int n, int D,
+                                   const T* __restrict__ pass_on, long pass_stride) {
     fb_pdl_launch_dependents();
     fb_pdl_wait();
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -114,6 +170,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ expert_out, long ex
     for (int k = 0; k < K; ++k) {
         const int at = pair_place[(size_t)row * K + k];
         if (at >= 0) acc = fmaf(share[(size_t)row * K + k], expert_out[(size_t)at * expert_stride + c], acc);
+        else if (pass_on) acc = fmaf(share[(size_t)row * K + k], fb_to_float(pass_on[(size_t)row * pass_stride + c]), acc);
     }
     if (shared_out) {
         float s = 0.0f;
@@ -155,11 +212,14 @@ FB_API int fb_moe_gather_rows(const void* h, long long h_stride, int dtype, cons
     return fb_check_launch("moe_gather_rows");
 }
 
+// rule 0: the `top` largest logits + bias, weights = softmax over the chosen; rule 1: scores = softmax over all E, the
+// `top` largest of score + bias, weights = chosen scores / their sum * weight_scale.
 // z: float32 router logits [n, >= E (+1)] (possibly split-K shares), as a product of the token rows with the stacked
 // router matrix left them; br: the router's bias or nullptr; gate_col: the column that holds w_gate . h (negative: none).
 FB_API int fb_moe_choose(const float* z, long long z_stride, int n_partials, long long partial_stride, const void* br,
                          int w_dtype, int gate_col, int n, int E, int K, int* chosen, float* share, float* gate,
-                         cudaStream_t stream) {
+                         int rule, float weight_scale, cudaStream_t stream) {
+    FB_REQUIRE(rule == 0 || rule == 1, "router: unknown rule %d", rule);
     FB_REQUIRE(n >= 0 && E > 0 && K > 0 && K <= E, "router: bad sizes n=%d experts=%d top=%d", n, E, K);
     FB_REQUIRE(E <= 32 * MOE_MAX_LOGITS_PER_LANE, "router: %d experts are more than %d", E, 32 * MOE_MAX_LOGITS_PER_LANE);
     FB_REQUIRE(K <= 32, "router: top = %d is more than 32", K);
@@ -169,7 +229,7 @@ FB_API int fb_moe_choose(const float* z, long long z_stride, int n_partials, lon
     if (n_partials < 1) n_partials = 1;
     FB_DISPATCH_DTYPE(w_dtype, TW,
         (fb_launch((moe_choose_kernel<TW>), dim3((n + 3) / 4), dim3(128), 0, stream, z, (long)z_stride, n_partials,
-                   (long)partial_stride, (const TW*)br, gate_col, n, E, K, chosen, share, gate)));
+                   (long)partial_stride, (const TW*)br, gate_col, n, E, K, chosen, share, gate, rule, weight_scale)));
     return fb_check_launch("moe_choose");
 }
 
@@ -190,11 +250,13 @@ FB_API int fb_moe_sort(const int* chosen, int pairs, int K, int E, int tile, int
 
 // Four columns a thread (D a multiple of 4, rows 16-byte aligned): a token's places and shares are fetched once per
 // four outputs and every row is read 16 bytes at a time.
+template <typename T>
 __global__ void moe_combine_vec_kernel(const float* __restrict__ expert_out, long expert_stride,
                                        const int* __restrict__ pair_place, const float* __restrict__ share, int K,
                                        const float* __restrict__ shared_out, int shared_partials,
                                        long shared_partial_stride, const float* __restrict__ gate,
-                                       float* __restrict__ out, int n, int D) {
+                                       float* __restrict__ out, int n, int D, const T* __restrict__ pass_on,
+                                       long pass_stride) {
     fb_pdl_launch_dependents();
     fb_pdl_wait();
     const int nvec = D >> 2;
@@ -204,9 +266,15 @@ __global__ void moe_combine_vec_kernel(const float* __restrict__ expert_out, lon
     float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     for (int k = 0; k < K; ++k) {
         const int at = pair_place[(size_t)row * K + k];
-        if (at < 0) continue;
+        if (at < 0 && !pass_on) continue;
         const float w = share[(size_t)row * K + k];
-        const float4 v = *reinterpret_cast<const float4*>(expert_out + (size_t)at * expert_stride + c);
+        float4 v;
+        if (at < 0) {                                  // an expert without weights: the token's own input
+            const T* src = pass_on + (size_t)row * pass_stride + c;
+            v = make_float4(fb_to_float(src[0]), fb_to_float(src[1]), fb_to_float(src[2]), fb_to_float(src[3]));
+        } else {
+            v = *reinterpret_cast<const float4*>(expert_out + (size_t)at * expert_stride + c);
+        }
         acc.x = fmaf(w, v.x, acc.x); acc.y = fmaf(w, v.y, acc.y); acc.z = fmaf(w, v.z, acc.z); acc.w = fmaf(w, v.w, acc.w);
     }
     if (shared_out) {
@@ -222,22 +290,29 @@ __global__ void moe_combine_vec_kernel(const float* __restrict__ expert_out, lon
     *reinterpret_cast<float4*>(out + (size_t)row * D + c) = acc;
 }
 
+// pass_on (optional, [n, D] rows `pass_stride` apart, dtype code `pass_dtype`): what a pair without a place (a chosen
+// expert that has no weights) contributes, times its share.
 FB_API int fb_moe_combine(const float* expert_out, long long expert_stride, const int* pair_place, const float* share,
                           int K, const float* shared_out, int shared_partials, long long shared_partial_stride,
-                          const float* gate, float* out, int n, int D, cudaStream_t stream) {
+                          const float* gate, float* out, int n, int D, const void* pass_on, int pass_dtype,
+                          long long pass_stride, cudaStream_t stream) {
     FB_REQUIRE(n >= 0 && D > 0 && K > 0, "moe_combine: bad sizes");
     if (n == 0) return 0;
+    if (!pass_on) pass_dtype = FB_F32;
     if (D % 4 == 0 && expert_stride % 4 == 0 && shared_partial_stride % 4 == 0 && (uintptr_t)expert_out % 16 == 0 &&
         (uintptr_t)out % 16 == 0 && (!shared_out || (uintptr_t)shared_out % 16 == 0)) {
         const size_t total4 = (size_t)n * (D / 4);
-        fb_launch(moe_combine_vec_kernel, dim3((unsigned)((total4 + 255) / 256)), dim3(256), 0, stream, expert_out,
-                  (long)expert_stride, pair_place, share, K, shared_out, shared_partials < 1 ? 1 : shared_partials,
-                  (long)shared_partial_stride, gate, out, n, D);
+        FB_DISPATCH_DTYPE(pass_dtype, T,
+            (fb_launch((moe_combine_vec_kernel<T>), dim3((unsigned)((total4 + 255) / 256)), dim3(256), 0, stream,
+                       expert_out, (long)expert_stride, pair_place, share, K, shared_out,
+                       shared_partials < 1 ? 1 : shared_partials, (long)shared_partial_stride, gate, out, n, D,
+                       (const T*)pass_on, (long)pass_stride)));
         return fb_check_launch("moe_combine");
     }
     const size_t total = (size_t)n * D;
-    fb_launch(moe_combine_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, expert_out,
-              (long)expert_stride, pair_place, share, K, shared_out, shared_partials < 1 ? 1 : shared_partials,
-              (long)shared_partial_stride, gate, out, n, D);
+    FB_DISPATCH_DTYPE(pass_dtype, T,
+        (fb_launch((moe_combine_kernel<T>), dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, expert_out,
+                   (long)expert_stride, pair_place, share, K, shared_out, shared_partials < 1 ? 1 : shared_partials,
+                   (long)shared_partial_stride, gate, out, n, D, (const T*)pass_on, (long)pass_stride)));
     return fb_check_launch("moe_combine");
 }

@@ -1,0 +1,75 @@
+// A short causal convolution over time that is added to its own input: every channel has `taps` weights of its own,
+//
+//     out_t = h_t + sum_j w[c][j] * h_(t - taps + 1 + j)          (the last tap is the current token's; zeros before
+//                                                                   the request's first token)
+//
+// for the rows of a step, which hold portions of several requests.  Inputs before a portion's start come from the
+// request's kept tail, the last taps - 1 inputs of the step before: `state` is a float32 array per request slot with the
+// tail at `tail_off`, laid out [taps - 1][D], oldest first.
+//
+//   time_conv         per (row, stretch of channels): the sum above in float32, rounded once to the output's dtype
+//   time_conv_tail    per (request, stretch of channels): the step's last taps - 1 inputs become the kept tail (a
+//                     portion shorter than that keeps the newest entries of the old tail in front of its own)
+//
+// The tail kernel runs after the convolution has read the old tail (stream order).
+#include "common.cuh"
+
+template <typename TW, typename TO>
+__global__ void __launch_bounds__(256)
+time_conv_kernel(const float* __restrict__ h, const TW* __restrict__ w, int taps, const float* __restrict__ state,
+                 long state_stride, long tail_off, const int* __restrict__ row_seq,
+                 const int* __restrict__ seq_q_start, const int* __restrict__ seq_slot, TO* __restrict__ out, int D) {
+    fb_pdl_launch_dependents();
+    fb_pdl_wait();
+    const int row = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= D) return;
+    const int seq = row_seq[row];
+    const int i = row - seq_q_start[seq];              // place within the step's portion of this request
+    const float* tail = state + (size_t)seq_slot[seq] * state_stride + tail_off;
+    float acc = h[(size_t)row * D + c];
+    for (int j = 0; j < taps; ++j) {
+        const int back = taps - 1 - j;
+        const float x = i - back >= 0 ? h[(size_t)(row - back) * D + c]
+                                      : tail[(size_t)(taps - 1 + i - back) * D + c];
+        acc = fmaf(fb_to_float(w[(size_t)c * taps + j]), x, acc);
+    }
+    out[(size_t)row * D + c] = fb_from_float<TO>(acc);
+}
+
+__global__ void __launch_bounds__(256)
+time_conv_tail_kernel(const float* __restrict__ h, int taps, float* __restrict__ state, long state_stride, long tail_off,
+                      const int* __restrict__ seq_q_start, const int* __restrict__ seq_q_len,
+                      const int* __restrict__ seq_slot, int D) {
+    fb_pdl_launch_dependents();
+    fb_pdl_wait();
+    const int seq = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= D) return;
+    const int L = seq_q_len[seq], start = seq_q_start[seq];
+    float* tail = state + (size_t)seq_slot[seq] * state_stride + tail_off;
+    // ascending m: an entry taken from the old tail lies above the one being written
+    for (int m = 0; m < taps - 1; ++m) {
+        const int src = L - (taps - 1) + m;
+        tail[(size_t)m * D + c] = src >= 0 ? h[(size_t)(start + src) * D + c] : tail[(size_t)(taps - 1 + src) * D + c];
+    }
+}
+
+// h: float32 [n, D] contiguous; w: [D, taps]; out: [n, D] contiguous in the engine's dtype.
+FB_API int fb_time_conv(const float* h, const void* w, int w_dtype, int taps, float* state, long long state_stride,
+                        long long tail_off, const int* row_seq, const int* seq_q_start, const int* seq_q_len,
+                        const int* seq_slot, int n_seqs, void* out, int out_dtype, int n, int D, cudaStream_t stream) {
+    FB_REQUIRE(n >= 0 && D > 0 && taps >= 1 && n_seqs >= 0, "time_conv: bad sizes");
+    FB_REQUIRE(taps == 1 || state, "time_conv: more than one tap needs the requests' kept inputs");
+    if (n == 0) return 0;
+    const unsigned stretches = (unsigned)((D + 255) / 256);
+    FB_REQUIRE(stretches <= 65535, "time_conv: width %d is too large", D);
+    FB_DISPATCH_DTYPE(w_dtype, TW, FB_DISPATCH_DTYPE(out_dtype, TO,
+        (fb_launch((time_conv_kernel<TW, TO>), dim3(n, stretches), dim3(256), 0, stream, h, (const TW*)w, taps,
+                   (const float*)state, (long)state_stride, (long)tail_off, row_seq, seq_q_start, seq_slot, (TO*)out, D))));
+    int rc = fb_check_launch("time_conv");
+    if (rc || taps < 2) return rc;
+    fb_launch(time_conv_tail_kernel, dim3(n_seqs, stretches), dim3(256), 0, stream, h, taps, state, (long)state_stride,
+              (long)tail_off, seq_q_start, seq_q_len, seq_slot, D);
+    return fb_check_launch("time_conv_tail");
+}

@@ -30,7 +30,7 @@ _SIGNATURES = {
     "fb_norm_add_rmsnorm": (I, [P, P, I, L, P, I, F, F, P, I, P, I, P, I, I, F, F, STREAM]),
     "fb_concat_cast": (I, [P, P, P, I, I, I, STREAM]),
     "fb_add_rmsnorm": (I, [P, P, I, I, L, P, I, P, I, P, I, I, F, F, STREAM]),
-    "fb_rope_table": (I, [P, P, P, P, I, I, STREAM]),
+    "fb_rope_table": (I, [P, P, P, P, I, I, F, STREAM]),
     "fb_rope_kv_write": (I, [P, L, I, L, P, L, P, L, P, L, I, I, P, P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, P, STREAM]),
     "fb_gate_mul": (I, [P, L, I, I, L, P, I, I, I, I, STREAM]),
     "fb_activation": (I, [P, L, I, I, L, P, I, I, I, I, STREAM]),
@@ -44,6 +44,7 @@ _SIGNATURES = {
     "fb_gemm_tc_add": (I, [P, L, P, L, P, L, I, I, I, I, P, STREAM]),
     "fb_gemm_tc": (I, [P, L, P, L, P, I, L, L, I, P, I, I, I, P, L, P, I, I, P, STREAM]),
     "fb_gemm_tc_grouped": (I, [P, L, P, L, I, P, I, P, I, L, I, I, I, I, P, STREAM]),
+    "fb_gemm_tc_grouped_gated": (I, [P, L, P, L, I, P, I, P, I, L, I, I, I, I, P, STREAM]),
     "fb_gemm_tc_gated": (I, [P, L, P, L, P, I, L, I, I, I, I, P, L, P, I, P, STREAM]),
     # attention_simt.cu
     "fb_paged_attention_simt": (I, [P, L, P, L, I, P, P, I, I, P, I, P, P, P, I, I, I, I, I, I, F, P, P, P, STREAM]),
@@ -55,11 +56,23 @@ _SIGNATURES = {
     "fb_gdr_recurrent": (I, [P, P, P, P, L, P, P, P, I, P, I, I, I, I, STREAM]),
     "fb_gdr_out_norm": (I, [P, P, L, I, L, I, P, I, F, P, I, I, I, I, STREAM]),
     # moe.cu
-    "fb_moe_choose": (I, [P, L, I, L, P, I, I, I, I, I, P, P, P, STREAM]),
+    "fb_moe_choose": (I, [P, L, I, L, P, I, I, I, I, I, P, P, P, I, F, STREAM]),
     "fb_moe_max_tiles": (I, [I, I, I]),
     "fb_moe_gather_rows": (I, [P, L, I, P, P, I, I, STREAM]),
     "fb_moe_sort": (I, [P, I, I, I, I, I, P, P, P, STREAM]),
-    "fb_moe_combine": (I, [P, L, P, P, I, P, I, L, P, P, I, I, STREAM]),
+    "fb_moe_combine": (I, [P, L, P, P, I, P, I, L, P, P, I, I, P, I, L, STREAM]),
+    # layer_norm.cu
+    "fb_add_layernorm": (I, [P, P, I, L, P, I, P, I, P, I, I, F, STREAM]),
+    "fb_depth_average": (I, [P, P, I, L, P, L, I, P, I, L, STREAM]),
+    # time_conv.cu
+    "fb_time_conv": (I, [P, P, I, I, P, L, L, P, P, P, P, I, P, I, I, I, STREAM]),
+    # linear_attention.cu
+    "fb_gla_prepare": (I, [P, L, I, L, P, P, I, I, F, F, P, P, I, I, I, I, STREAM]),
+    "fb_gla_recurrent": (I, [P, P, P, L, P, P, P, I, P, I, I, I, STREAM]),
+    # latent_attention.cu
+    "fb_mla_latents": (I, [P, L, I, L, I, P, P, I, I, I, P, I, F, P, P, I, P, P, P, I, P, P, I, I, I, I, P, STREAM]),
+    "fb_head_linear": (I, [P, I, L, L, I, L, P, I, P, I, L, L, P, L, I, L, I, P, P, I, I, I, I, I, I, STREAM]),
+    "fb_rope_neighbours": (I, [P, L, P, P, I, I, I, I, STREAM]),
     # diff_attention.cu
     "fb_qkv_bias_cache_write": (I, [P, L, I, L, P, I, P, L, I, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, I, P,
                                     STREAM]),

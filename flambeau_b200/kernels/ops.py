@@ -197,7 +197,9 @@ def diff_attention_simt(q, out, gate, cache, positions, row_seq, nh: int, nkv: i
         float(scale), float(lam), float(eps), float(out_scale), status.data_ptr(), _stream()), "diff_attention_simt")
 
 
-def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> None:
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
+               magnitude: float = 1.0) -> None:
+    """cos[t, i], sin[t, i] = magnitude * cos / sin(positions[t] * inv_freq[i]), the angle formed in float64."""
     _cuda(positions, inv_freq, cos, sin)
     _i32(positions, "positions")
     n, half = positions.numel(), inv_freq.numel()
@@ -205,7 +207,7 @@ def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, cos: torch.Tenso
             or cos.numel() < n * half or sin.numel() < n * half:
         raise KernelError("rope_table: bad arguments")
     check(lib().fb_rope_table(positions.data_ptr(), inv_freq.data_ptr(), cos.data_ptr(), sin.data_ptr(), n, half,
-                              _stream()), "rope_table")
+                              float(magnitude), _stream()), "rope_table")
 
 
 def rope_kv_write(q_in, q_out, k, v, cos, sin, half: int, positions, row_seq, block_table, k_pool, v_pool,
@@ -577,6 +579,43 @@ def gemm_tc_grouped(a: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, 
           "gemm_tc_grouped", (M, N, K))
 
 
+def gemm_tc_grouped_gated(a: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, tile: int, out: torch.Tensor,
+                          status: torch.Tensor, activation: str) -> None:
+    """out[m, c] = act(g_c) * u_c with (g_0, u_0, g_1, u_1, ...) = a[m] @ w[tile_group[m // tile]]^T on the tcgen05
+    kernel: w [groups, 2 I, K] stacks every group's gate and up rows alternately, out has I columns."""
+    _cuda(a, w, tile_group, out, status)
+    _i32(tile_group, "tile_group")
+    groups, N, K = w.shape
+    M = out.shape[0]
+    if a.shape[0] != M or a.shape[1] != K or out.shape[1] * 2 != N or tile_group.numel() * tile < M:
+        raise KernelError("grouped gated gemm: shapes do not agree")
+    check(lib().fb_gemm_tc_grouped_gated(a.data_ptr(), _rows(a), w.data_ptr(), K, groups, tile_group.data_ptr(),
+                                         int(tile), out.data_ptr(), dtype_code(out), _rows(out), M, N, K,
+                                         activation_code(activation), status.data_ptr(), _stream()),
+          "gemm_tc_grouped_gated", (M, N, K))
+
+
+def grouped_gated_linear(a: torch.Tensor, row_index, w: torch.Tensor, tile_group: torch.Tensor, tile: int,
+                         out: torch.Tensor, activation: str, ctx) -> None:
+    """out[m] = act(gate) * up of a[row_index[m]] under the weights of the row tile's group (w [groups, 2 I, K], gate
+    and up rows alternating): on the tcgen05 kernel with the activation in its epilogue for bfloat16 operands, else
+    the float32-FMA grouped product followed by the activation kernel."""
+    if grouped_tc_supported(a, w, out):
+        with ctx.ws.scope():
+            side = a
+            if row_index is not None:
+                side = ctx.ws.alloc((out.shape[0], a.shape[1]), a.dtype)
+                gather_rows(a, row_index, side)
+            gemm_tc_grouped_gated(side, w, tile_group, tile, out, ctx.runtime.status, activation)
+        return
+    if tile not in (16, 64):
+        raise KernelError(f"grouped gemm: the float32-FMA kernel takes tiles of 16 or 64 rows, not {tile}")
+    with ctx.ws.scope():
+        gu = ctx.ws.alloc((out.shape[0], w.shape[1]), torch.float32)
+        gemm_simt_grouped(a, row_index, w, tile_group, tile, gu, None)
+        gate_mul(gu, out, activation=activation)
+
+
 def grouped_linear(a: torch.Tensor, row_index, w: torch.Tensor, tile_group: torch.Tensor, tile: int,
                    out: torch.Tensor, activation_name=None, ctx=None) -> None:
     """out[m] = act(a[row_index[m]] @ w[tile_group[m // tile]]^T) with w [groups, N, K]: the product of routed
@@ -890,10 +929,17 @@ def gdr_out_norm(o, proj, gate_off: int, weight, eps: float, out, H: int, dv: in
 # ---------------------------------------------------------------------------
 # routed experts
 # ---------------------------------------------------------------------------
+ROUTER_RULES = {"softmax_of_chosen": 0, "softmax_of_all": 1}
+
+
 def moe_choose(z, bias, gate_col: int, experts: int, top: int, chosen, share, gate, n_partials: int = 1,
-               partial_stride: int = 0) -> None:
+               partial_stride: int = 0, rule: str = "softmax_of_chosen", weight_scale: float = 1.0) -> None:
     """Per token: the `top` experts with the largest logits z[:, :experts] + bias (float32; z possibly split-K
-    shares), their softmax weights, and (gate_col >= 0) gate = sigmoid(z[:, gate_col])."""
+    shares), their softmax weights, and (gate_col >= 0) gate = sigmoid(z[:, gate_col]).  rule 'softmax_of_all':
+    scores = softmax(z) over all experts, the `top` largest of score + bias are chosen, and the weights are the chosen
+    scores over their sum, times `weight_scale`."""
+    if rule not in ROUTER_RULES:
+        raise KernelError(f"router: rule '{rule}' is not one of {sorted(ROUTER_RULES)}")
     _cuda(z, bias, chosen, share, gate)
     n = z.shape[0]
     if z.dtype != torch.float32 or tuple(chosen.shape) != (n, top) or chosen.dtype != torch.int32 \
@@ -901,7 +947,8 @@ def moe_choose(z, bias, gate_col: int, experts: int, top: int, chosen, share, ga
         raise KernelError("router: bad shapes")
     check(lib().fb_moe_choose(z.data_ptr(), _rows(z), int(n_partials), int(partial_stride), _ptr(bias),
                               dtype_code(bias) if bias is not None else 0, int(gate_col), n, int(experts), int(top),
-                              chosen.data_ptr(), share.data_ptr(), _ptr(gate), _stream()), "moe_choose")
+                              chosen.data_ptr(), share.data_ptr(), _ptr(gate), ROUTER_RULES[rule],
+                              float(weight_scale), _stream()), "moe_choose")
 
 
 def moe_max_tiles(pairs: int, experts: int, tile: int) -> int:
@@ -918,9 +965,13 @@ def moe_sort(chosen, experts: int, tile: int, place_token, pair_place, tile_expe
 
 
 def moe_combine(expert_out, pair_place, share, shared_out, shared_partials: int, shared_partial_stride: int, gate,
-                out, n: int) -> None:
-    """out[t] = sum_k share[t, k] * expert_out[pair_place[t, k]] + gate[t] * sum of shared_out's shares."""
-    _cuda(expert_out, pair_place, share, shared_out, gate, out)
+                out, n: int, pass_on=None) -> None:
+    """out[t] = sum_k share[t, k] * expert_out[pair_place[t, k]] + gate[t] * sum of shared_out's shares (gate None:
+    1).  pass_on ([n, D], optional): a pair without a place (an expert that has no weights) contributes
+    share * pass_on[t]."""
+    _cuda(expert_out, pair_place, share, shared_out, gate, out, pass_on)
+    if pass_on is not None and pass_on.shape[1] != out.shape[1]:
+        raise KernelError("moe_combine: the rows handed on must have the output's width")
     D = out.shape[1]
     K = share.shape[1]
     if expert_out.dtype != torch.float32 or out.dtype != torch.float32 or not out.is_contiguous() \
@@ -929,4 +980,155 @@ def moe_combine(expert_out, pair_place, share, shared_out, shared_partials: int,
         raise KernelError("moe_combine: float32 rows of the output's width wanted")
     check(lib().fb_moe_combine(expert_out.data_ptr(), _rows(expert_out), pair_place.data_ptr(), share.data_ptr(), K,
                                _ptr(shared_out), int(shared_partials), int(shared_partial_stride), _ptr(gate),
-                               out.data_ptr(), int(n), D, _stream()), "moe_combine")
+                               out.data_ptr(), int(n), D, _ptr(pass_on),
+                               dtype_code(pass_on) if pass_on is not None else 0,
+                               _rows(pass_on) if pass_on is not None else 0, _stream()), "moe_combine")
+
+
+# ---------------------------------------------------------------------------
+# a norm that centres; a weighted mean over depth; a convolution over time in front of a sublayer
+# ---------------------------------------------------------------------------
+def add_layer_norm(x: torch.Tensor, delta, weight: torch.Tensor, eps: float, out: torch.Tensor, rows=None,
+                   n_partials: int = 1, n_rows: int | None = None, partial_stride: int = 0) -> None:
+    """out[j] = (v - mean v) / sqrt(var v + eps) * weight with v = x[r] + sum_p delta_p[r], r = rows[j] or j; without
+    `rows` the sum is also written back to x.  delta: float32 [n, H] or the first of n_partials slabs."""
+    _cuda(x, delta, weight, out, rows)
+    _i32(rows, "rows")
+    H = x.shape[1]
+    n_out = rows.numel() if rows is not None else (x.shape[0] if n_rows is None else n_rows)
+    if x.dtype != torch.float32 or not x.is_contiguous() or not out.is_contiguous() or out.shape[-1] != H \
+            or weight.numel() != H or out.shape[0] < n_out:
+        raise KernelError("add_layer_norm: bad shapes")
+    stride = 0
+    if delta is not None:
+        if delta.dtype != torch.float32 or not delta.is_contiguous() or delta.shape[-1] != H:
+            raise KernelError("add_layer_norm: delta must be contiguous float32 with the stream's width")
+        if n_partials > 1:
+            stride = int(partial_stride)
+            if stride <= 0:
+                raise KernelError("add_layer_norm: several slabs need their stride")
+    check(lib().fb_add_layernorm(x.data_ptr(), _ptr(delta), int(n_partials) if delta is not None else 0, stride,
+                                 weight.data_ptr(), dtype_code(weight), out.data_ptr(), dtype_code(out), _ptr(rows),
+                                 n_out, H, float(eps), _stream()), "add_layer_norm")
+
+
+def depth_average(x: torch.Tensor, delta, n_partials: int, partial_stride: int, history: torch.Tensor, count: int,
+                  weights: torch.Tensor, n: int) -> None:
+    """history[count - 1] = x + sum of delta's slabs; x = sum_{j < count} weights[j] * history[j], over the first n
+    rows.  x float32 [>= n, H] contiguous; history float32 [slots, rows, H] contiguous."""
+    _cuda(x, delta, history, weights)
+    H = x.shape[1]
+    if x.dtype != torch.float32 or not x.is_contiguous() or history.dtype != torch.float32 \
+            or not history.is_contiguous() or history.shape[-1] != H or history.shape[1] < n \
+            or not 1 <= count <= history.shape[0] or weights.numel() < count or not weights.is_contiguous():
+        raise KernelError("depth_average: bad shapes")
+    if delta is not None and (delta.dtype != torch.float32 or not delta.is_contiguous() or delta.shape[-1] != H):
+        raise KernelError("depth_average: delta must be contiguous float32 with the stream's width")
+    check(lib().fb_depth_average(x.data_ptr(), _ptr(delta), int(n_partials) if delta is not None else 0,
+                                 int(partial_stride) if n_partials > 1 else 0, history.data_ptr(), history.stride(0),
+                                 int(count), weights.data_ptr(), dtype_code(weights), int(n) * H, _stream()),
+          "depth_average")
+
+
+def time_conv(h: torch.Tensor, w: torch.Tensor, state, tail_off: int, batch, out: torch.Tensor, n: int) -> None:
+    """out[t] = h[t] + sum_j w[:, j] * h[t - taps + 1 + j] per request (csrc/time_conv.cu); h float32 [n, D]; w
+    [D, taps]; state float32 [slots, floats] with the kept inputs [taps - 1, D] at tail_off, updated for the next step."""
+    _cuda(h, w, state, out)
+    D, taps = w.shape
+    if h.dtype != torch.float32 or not h.is_contiguous() or h.shape[1] != D or not out.is_contiguous() \
+            or out.shape[1] != D or out.shape[0] < n or h.shape[0] < n or not w.is_contiguous():
+        raise KernelError("time_conv: bad shapes")
+    if taps > 1 and (state is None or state.dtype != torch.float32 or state.dim() != 2 or not state.is_contiguous()
+                     or state.shape[1] < tail_off + (taps - 1) * D):
+        raise KernelError("time_conv: the state slot is too small for the kept inputs")
+    check(lib().fb_time_conv(h.data_ptr(), w.data_ptr(), dtype_code(w), int(taps), _ptr(state),
+                             state.stride(0) if state is not None else 0, int(tail_off), batch.row_seq.data_ptr(),
+                             batch.seq_q_start_d.data_ptr(), batch.seq_q_len_d.data_ptr(), batch.seq_slot_d.data_ptr(),
+                             batch.n_seqs, out.data_ptr(), dtype_code(out), int(n), D, _stream()), "time_conv")
+
+
+# ---------------------------------------------------------------------------
+# gated linear attention
+# ---------------------------------------------------------------------------
+def gla_prepare(proj, w2, b2, tau: float, q_scale: float, qkv, decay, H: int, dk: int, dv: int, n_partials: int = 1,
+                partial_stride: int = 0) -> None:
+    """The step's tokens made ready for the recurrence (csrc/linear_attention.cu): proj float32 rows
+    [q | k | v | gate | middle] (possibly shares); w2 [H * dk, R], b2 [H * dk]; qkv float32 [n, 2 H dk + H dv];
+    decay float32 [n, H dk]."""
+    _cuda(proj, w2, b2, qkv, decay)
+    n = proj.shape[0]
+    R = w2.shape[1]
+    if proj.dtype != torch.float32 or tuple(w2.shape) != (H * dk, R) or b2.numel() != H * dk or w2.dtype != b2.dtype \
+            or not w2.is_contiguous() or not b2.is_contiguous() or tuple(qkv.shape) != (n, 2 * H * dk + H * dv) \
+            or tuple(decay.shape) != (n, H * dk) \
+            or any(t.dtype != torch.float32 or not t.is_contiguous() for t in (qkv, decay)):
+        raise KernelError("linear attention: bad shapes or dtypes")
+    check(lib().fb_gla_prepare(proj.data_ptr(), _rows(proj), int(n_partials), int(partial_stride), w2.data_ptr(),
+                               b2.data_ptr(), dtype_code(w2), R, float(tau), float(q_scale), qkv.data_ptr(),
+                               decay.data_ptr(), n, H, dk, dv, _stream()), "gla_prepare")
+
+
+def gla_recurrent(qkv, decay, state, batch, o, H: int, dk: int, dv: int) -> None:
+    """S <- diag(alpha) S + k v^T; o = S^T q over the step's tokens of every request, the state [H][dv][dk] at the
+    start of the request's slot."""
+    _cuda(qkv, decay, state, o)
+    if o.dtype != torch.float32 or not o.is_contiguous() or o.shape[1] != H * dv or state.dtype != torch.float32 \
+            or state.dim() != 2 or not state.is_contiguous() or state.shape[1] < H * dk * dv:
+        raise KernelError("linear attention: bad output or state")
+    check(lib().fb_gla_recurrent(qkv.data_ptr(), decay.data_ptr(), state.data_ptr(), state.stride(0),
+                                 batch.seq_q_start_d.data_ptr(), batch.seq_q_len_d.data_ptr(),
+                                 batch.seq_slot_d.data_ptr(), batch.n_seqs, o.data_ptr(), H, dk, dv, _stream()),
+          "gla_recurrent")
+
+
+# ---------------------------------------------------------------------------
+# latent attention
+# ---------------------------------------------------------------------------
+def mla_latents(proj, Rq: int, wq, cq, kv_off: int, Rc: int, r: int, wkv, eps: float, cos, sin, half: int, cache,
+                positions, row_seq, status, n_partials: int = 1, partial_stride: int = 0) -> None:
+    """cq = rmsnorm(proj[:, :Rq]) * wq; with a writable cache also the token's cache row [rmsnorm(proj[:, kv_off:
+    kv_off + Rc]) * wkv | rot(proj[:, kv_off + Rc : kv_off + Rc + r])] (csrc/latent_attention.cu)."""
+    _cuda(proj, wq, cq, wkv, cos, sin, positions, row_seq, status)
+    n = proj.shape[0]
+    if proj.dtype != torch.float32 or wq.numel() != Rq or tuple(cq.shape) != (n, Rq) or not cq.is_contiguous():
+        raise KernelError("latent attention: bad shapes")
+    pool = cache.k_pool if cache is not None and cache.writable else None
+    if pool is not None:
+        if tuple(pool.shape[1:]) != (1, cache.page_size, Rc + r) or not pool.is_contiguous() or pool.dtype != cq.dtype \
+                or wkv.numel() != Rc or wkv.dtype != wq.dtype or proj.shape[1] < kv_off + Rc + r:
+            raise KernelError("latent attention: the cache rows do not fit the latent")
+    check(lib().fb_mla_latents(
+        proj.data_ptr(), _rows(proj), int(n_partials), int(partial_stride), Rq, wq.data_ptr(), cq.data_ptr(), kv_off,
+        Rc, r, _ptr(wkv), dtype_code(wq), float(eps), _ptr(cos), _ptr(sin), half, _ptr(positions), _ptr(row_seq),
+        _ptr(cache.block_table) if pool is not None else 0, cache.block_table.stride(0) if pool is not None else 0,
+        _ptr(cache.table_base) if pool is not None else 0, _ptr(pool), dtype_code(cq),
+        cache.page_size if pool is not None else 1, pool.shape[0] if pool is not None else 0, n, status.data_ptr(),
+        _stream()), "mla_latents")
+
+
+def head_linear(a, a_head: int, w, out, o_head: int, n: int, n_partials: int = 1, partial_stride: int = 0, gate=None,
+                gate_off: int = 0, gate_partials: int = 1, gate_partial_stride: int = 0, cos=None, sin=None,
+                half: int = 0, rot: int = 0) -> None:
+    """out[t, h*o_head + c] = sum_k w[h, c, k] * a[t, h*a_head + k] for every head h (w [H, N, K]); `a` may be the
+    first of float32 shares.  gate (float32 rows, possibly shares): the result is multiplied by
+    sigmoid(gate[t, gate_off + h*N + c]).  rot > 0: columns K .. K+rot of a's head go, their first 2*half dimensions
+    turned pairwise by (cos, sin), to columns N .. N+rot of out's head."""
+    _cuda(a, w, out, gate, cos, sin)
+    H, N, K = w.shape
+    if not w.is_contiguous() or a.shape[0] < n or out.shape[0] < n:
+        raise KernelError("head_linear: bad shapes")
+    check(lib().fb_head_linear(a.data_ptr(), dtype_code(a), _rows(a), int(a_head), int(n_partials), int(partial_stride),
+                               w.data_ptr(), dtype_code(w), out.data_ptr(), dtype_code(out), _rows(out), int(o_head),
+                               _ptr(gate), _rows(gate) if gate is not None else 0, int(gate_partials),
+                               int(gate_partial_stride), int(gate_off), _ptr(cos), _ptr(sin), int(half), int(rot),
+                               int(n), H, N, K, _stream()), "head_linear", (n * H, N, K))
+
+
+def rope_neighbours(x, cos, sin, half: int, heads: int, head_dim: int) -> None:
+    """In place on float32 rows [n, heads * head_dim]: dimensions (2i, 2i + 1), i < half, of every head turned by the
+    tables' angles."""
+    _cuda(x, cos, sin)
+    if x.dtype != torch.float32 or x.shape[1] < heads * head_dim:
+        raise KernelError("rope_neighbours: float32 rows of heads * head_dim wanted")
+    check(lib().fb_rope_neighbours(x.data_ptr(), _rows(x), cos.data_ptr(), sin.data_ptr(), int(half), int(heads),
+                                   int(head_dim), x.shape[0], _stream()), "rope_neighbours")

@@ -61,9 +61,11 @@ class DecoderModel:
     def cache_plans(self) -> list:
         plans = []
         for call in self.order:
-            mixer = self.layers[call.layer].mixer
-            plans.append(CallPlan(kv=mixer.cache_requirement(), state=mixer.state_requirement(),
-                                  cache_from=call.cache_from))
+            block = self.layers[call.layer]
+            mixer = block.mixer
+            # (a block that keeps state beside its mixer's, such as the inputs a convolution still needs, says so)
+            state = block.state_requirement() if hasattr(block, "state_requirement") else mixer.state_requirement()
+            plans.append(CallPlan(kv=mixer.cache_requirement(), state=state, cache_from=call.cache_from))
         return plans
 
     # ---- one step -------------------------------------------------------------

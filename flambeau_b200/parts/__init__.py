@@ -1,6 +1,6 @@
 """Parts: import the built-in ones so that they are registered."""
-from . import (attention, block, diff_attention, embedding, feedforward, gated_delta, moe, norms, parallel,  # noqa: F401
-               positions, reentry)
+from . import (attention, block, diff_attention, embedding, feedforward, gated_delta, latent_attention,  # noqa: F401
+               linear_attention, moe, norms, parallel, positions, reentry, time_conv)
 from .base import (FeedForward, KVRequirement, Mixer, Norm, Part, PositionEncoding, StateRequirement,  # noqa: F401
                    TensorSpec)
 from .spec import (LayerCall, ModelSpec, PartSpec, build_part, part_class, register_part,  # noqa: F401

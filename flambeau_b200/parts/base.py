@@ -20,7 +20,10 @@ Categories and the method each must have:
   mixer          forward(ctx, h, out, call); cache_requirement() -> KVRequirement | None;
                  state_requirement() -> StateRequirement | None.
   feed_forward   forward(ctx, h, out).
-  block          forward(ctx, stream, call); mixer and feed_forward attributes.
+  block          forward(ctx, stream, call); mixer and feed_forward attributes; optionally state_requirement()
+                 where the block keeps state of its own beside its mixer's.
+  input_map      forward(ctx, h, out, state, offset): what a sublayer reads, made from the normalised rows h
+                 (float32) into `out` (engine dtype); state_floats(): float32 numbers it keeps per request.
   embedding      forward(ctx, token_ids, x).
   head           forward(ctx, h_rows, logits).
 
@@ -43,6 +46,7 @@ class KVRequirement:
     head_dim: int            # elements of a key row (per key/value head)
     window: int = 0          # 0 = all earlier keys stay live; W > 0 = only the last W
     v_head_dim: int = 0      # elements of a value row where it differs from a key row (0: the same)
+    values_in_keys: bool = False   # the key rows are the values as well: one pool serves as both, nothing is kept twice
 
     @property
     def value_dim(self) -> int:

@@ -1,8 +1,10 @@
 """How a layer arranges its norms, mixer and feed-forward around the stream."""
 from __future__ import annotations
 
+import torch
+
 from ..kernels import ops
-from .base import Part
+from .base import Part, StateRequirement, TensorSpec
 from .spec import PartSpec, build_part, register_part
 
 
@@ -37,40 +39,138 @@ class ResidualStream:
 class PreNormBlock(Part):
     """x = x + mixer(norm1(x)); x = x + feed_forward(norm2(x))
     (crates/models/qwen35-v2/src/model.rs:25-42).  `feed_forward` (with its norm) may be None: the layer then ends
-    behind the mixer."""
+    behind the mixer.  `mixer_input` / `feed_forward_input` (parts of category 'input_map', optional): what the
+    sublayer reads is made from the normalised rows by that part (a short convolution over time, say); the norm then
+    leaves its rows in float32, so that the map's result is rounded once.  What such parts keep per request lies in
+    the layer call's state slot behind the mixer's own state (float32 numbers: [mixer | mixer_input |
+    feed_forward_input])."""
     graph_safe = True
     category = "block"
 
     def __init__(self, runtime=None, prefix="", *, mixer: PartSpec, mixer_norm: PartSpec,
-                 feed_forward: PartSpec | None = None, feed_forward_norm: PartSpec | None = None):
+                 feed_forward: PartSpec | None = None, feed_forward_norm: PartSpec | None = None,
+                 mixer_input: PartSpec | None = None, feed_forward_input: PartSpec | None = None):
         super().__init__(runtime, prefix)
         self.mixer = build_part(mixer, runtime)
         self.mixer_norm = build_part(mixer_norm, runtime)
-        self.feed_forward = self.feed_forward_norm = None
+        self.mixer_input = build_part(mixer_input, runtime) if mixer_input is not None else None
+        self.feed_forward = self.feed_forward_norm = self.feed_forward_input = None
         if feed_forward is not None:
             if feed_forward_norm is None:
                 raise ValueError("a feed-forward behind a norm needs that norm")
             self.feed_forward = build_part(feed_forward, runtime)
             self.feed_forward_norm = build_part(feed_forward_norm, runtime)
+            self.feed_forward_input = build_part(feed_forward_input, runtime) if feed_forward_input is not None else None
+        elif feed_forward_input is not None:
+            raise ValueError("an input map for a feed-forward that the layer does not have")
+        # where the input maps' numbers begin in the layer call's state slot
+        own = self.mixer.state_requirement()
+        kept = [m.state_floats() for m in (self.mixer_input, self.feed_forward_input) if m is not None]
+        self._state = own
+        self._offsets = (0, 0)
+        if sum(kept) > 0:
+            if own is not None and (own.dtype != "float32" or len(own.shape) != 1):
+                raise ValueError("input maps keep their numbers behind the mixer's state, which must then be one flat "
+                                 "float32 array")
+            base = own.shape[0] if own is not None else 0
+            first = self.mixer_input.state_floats() if self.mixer_input is not None else 0
+            self._offsets = (base, base + first)
+            self._state = StateRequirement((base + sum(kept),), "float32")
 
     def children(self):
-        return [p for p in (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward) if p is not None]
+        return [p for p in (self.mixer_norm, self.mixer_input, self.mixer, self.feed_forward_norm,
+                            self.feed_forward_input, self.feed_forward) if p is not None]
+
+    def state_requirement(self):
+        return self._state
+
+    def _normed_input(self, ctx, norm, input_map, offset, stream, call, h):
+        """h = input_map(norm(x + pending)) (or the norm alone), the pending output added to the stream on the way."""
+        if input_map is None:
+            norm.add_norm(ctx, stream.x, stream.pending, h, n_partials=stream.pending_slabs,
+                          delta_norm=stream.pending_norm)
+            return
+        with ctx.ws.scope():
+            rows = ctx.ws.alloc((ctx.n_tokens, stream.x.shape[1]), torch.float32)
+            norm.add_norm(ctx, stream.x, stream.pending, rows, n_partials=stream.pending_slabs,
+                          delta_norm=stream.pending_norm)
+            state = ctx.cache(call).state
+            input_map.forward(ctx, rows, h, state.view(state.shape[0], -1) if state is not None else None, offset)
 
     def forward(self, ctx, stream: ResidualStream, call) -> None:
         h, delta = ctx.normed, ctx.delta
         ctx.stream_x = stream.x
-        self.mixer_norm.add_norm(ctx, stream.x, stream.pending, h, n_partials=stream.pending_slabs,
-                                 delta_norm=stream.pending_norm)
+        self._normed_input(ctx, self.mixer_norm, self.mixer_input, self._offsets[0], stream, call, h)
         stream.pending_norm = None
         ctx.pending_slabs = 1                 # a part that leaves split-K shares in ctx.delta_slabs says how many
         self.mixer.forward(ctx, h, delta, call)
         stream.pending, stream.pending_slabs = delta, ctx.pending_slabs
         if self.feed_forward is not None:
-            self.feed_forward_norm.add_norm(ctx, stream.x, stream.pending, h, n_partials=stream.pending_slabs)
+            self._normed_input(ctx, self.feed_forward_norm, self.feed_forward_input, self._offsets[1], stream, call, h)
             ctx.pending_slabs = 1
             self.feed_forward.forward(ctx, h, delta)
             stream.pending, stream.pending_slabs = delta, ctx.pending_slabs
         ctx.stream_x = None                   # another kind of block decides for itself whether parts may add to its stream
+
+
+class DepthAveragedBlock(Part):
+    """A block whose result is not handed on as it is: the model keeps what every block so far has produced, X_0 (the
+    embedding output) to X_depth-1 (this block's result, the stream with everything added), and the next block reads
+    x = sum_j w[j] X_j with this block's own learned weights `<prefix><weight_name>` [depth].  `block` is the block
+    that does the layer's work; `depth` counts the kept results including this block's; `slots` is how many the
+    model keeps in all (its layer calls + 1).  The kept results live for one step (float32 [slots, rows, width])."""
+    graph_safe = True
+    category = "block"
+    HISTORY = "depth_average.history"
+
+    def __init__(self, runtime=None, prefix="", *, block: PartSpec, depth: int, slots: int, width: int,
+                 weight_name: str = "dwa"):
+        super().__init__(runtime, prefix)
+        self.inner = build_part(block, runtime)
+        self.depth, self.slots, self.width, self.weight_name = int(depth), int(slots), int(width), weight_name
+        if not 2 <= self.depth <= self.slots:
+            raise ValueError(f"depth = {self.depth} of {self.slots} kept results")
+        self.weight = None
+
+    @property
+    def mixer(self):
+        return self.inner.mixer
+
+    @property
+    def feed_forward(self):
+        return self.inner.feed_forward
+
+    def state_requirement(self):
+        inner = self.inner
+        return inner.state_requirement() if hasattr(inner, "state_requirement") else inner.mixer.state_requirement()
+
+    def children(self):
+        return [self.inner]
+
+    def own_tensor_specs(self):
+        # (the newest result gets most of the weight, so that random weights still behave like a residual stream)
+        return {self.prefix + self.weight_name: TensorSpec((self.depth,), init=("depth_mix", 0.1))}
+
+    def own_bind(self, tensors):
+        self.weight = tensors[self.prefix + self.weight_name].contiguous()
+
+    def own_weights(self):
+        return [self.weight]
+
+    def forward(self, ctx, stream: ResidualStream, call) -> None:
+        n = ctx.n_tokens
+        history = ctx.shared.get(self.HISTORY)
+        if history is None:
+            stream.settle(ctx)
+            history = ctx.shared[self.HISTORY] = ctx.step_alloc((self.slots, n, self.width), torch.float32)
+            history[0].copy_(stream.x[:n])
+        self.inner.forward(ctx, stream, call)
+        if stream.pending_norm is not None:
+            stream.settle(ctx)
+        pending = stream.pending if stream.pending_slabs > 0 else None
+        ops.depth_average(stream.x, pending, stream.pending_slabs if pending is not None else 0,
+                          ctx.delta_slabs.stride(0), history, self.depth, self.weight, n)
+        stream.pending, stream.pending_slabs, stream.pending_norm = None, 0, None
 
 
 class SandwichNormBlock(Part):
@@ -121,3 +221,4 @@ class SandwichNormBlock(Part):
 
 register_part("block", "pre_norm", PreNormBlock)
 register_part("block", "sandwich_norm", SandwichNormBlock)
+register_part("block", "depth_averaged", DepthAveragedBlock)

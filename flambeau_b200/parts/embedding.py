@@ -34,17 +34,17 @@ class TokenEmbedding(Part):
 
 
 class LMHead(Part):
-    """logits = h W^T in float32, for the wanted rows only; a tied head reuses
+    """logits = h W^T (times `scale`) in float32, for the wanted rows only; a tied head reuses
     the embedding table (crates/forward/src/core/composites/output_head.rs:90-132;
     crates/models/qwen35-v2/src/loader.rs:219-223)."""
     graph_safe = True
     category = "head"
 
     def __init__(self, runtime=None, prefix="", *, vocab: int, width: int, tied_to: str | None = None,
-                 init_std: float = 0.02, weight_name: str = "weight"):
+                 init_std: float = 0.02, weight_name: str = "weight", scale: float = 1.0):
         super().__init__(runtime, prefix)
         self.vocab, self.width, self.tied_to, self.init_std = int(vocab), int(width), tied_to, init_std
-        self.weight_name = weight_name
+        self.weight_name, self.scale = weight_name, float(scale)
         self.proj = None
 
     def own_tensor_specs(self):
@@ -59,6 +59,8 @@ class LMHead(Part):
 
     def forward(self, ctx, h_rows, logits):
         self.proj(ctx, h_rows, logits)
+        if self.scale != 1.0:
+            logits.mul_(self.scale)          # float32, the wanted rows only
 
 
 register_part("embedding", "token_embedding", TokenEmbedding)

@@ -5,23 +5,31 @@ import torch
 
 from ..kernels import ops
 from .base import FeedForward, TensorSpec
-from .linear import Linear, concat_rows
-from .spec import register_part
+from .linear import Linear, concat_rows, interleave_rows
+from .spec import PartSpec, build_part, register_part
 
 
 class RoutedExperts(FeedForward):
-    """d = sum over the token's `top` experts of share_e * Wdown_e act(Wup_e h)  (+ gate * shared(h))
+    """d = sum over the token's `top` experts of share_e * expert_e(h)  (+ a shared expert)
 
-    Router logits z = Wr h + br are float32; the `top` experts with the largest logits are chosen (the lower index
-    wins a tie) and their shares are the softmax over the chosen logits only.  Experts have no biases and no gate
-    map; `activation` is one of kernels.ops.PLAIN_ACTIVATIONS.  With `shared_inner`, one more expert of that inner
-    size runs for every token and is added times sigmoid(w_sg . h), one number per token.
+    Router logits z = Wr h are float32.  Two rules turn them into a choice and shares:
+      'softmax_of_chosen' (the default): the `top` experts with the largest z + br are chosen (the lower index wins a
+        tie) and their shares are the softmax over the chosen logits only;
+      'softmax_of_all': scores s = softmax(z) over all experts; the `top` largest of s + br are chosen (br only moves
+        the choice); the shares are the chosen scores themselves over their sum (+ 1e-20), times `weight_scale`.
+    An expert is Wdown act(Wup h) with `activation` one of kernels.ops.PLAIN_ACTIVATIONS, or, with `gated`,
+    Wdown (act(Wgate h) * (Wup h)) with `activation` one of kernels.ops.ACTIVATIONS; experts have no biases.
+    `identity` (a count): that many more router outputs, behind the experts', stand for experts without weights
+    whose output is their input h itself (times the share).
+    A shared expert runs for every token and is added: with `shared_inner`, one of the experts' plain form times
+    sigmoid(w_sg . h), one number per token; with `shared` (a feed-forward PartSpec), that part's output as it is.
 
-    Tensors behind the prefix: e<i>.up [inner, width], e<i>.down [width, inner], router [experts, width], router.b
-    [experts], and with a shared expert shared.up, shared.down, shared.sg [1, width].
+    Tensors behind the prefix: e<i>.up [inner, width], e<i>.down [width, inner] (gated: e<i>.gate as well), router
+    [experts + identity, width], `bias_name` [experts + identity] (if router_bias), and with `shared_inner`
+    shared.up, shared.down, shared.sg [1, width].
 
-    How a step runs: the router's logits and the shared expert's gate as one product, the choice (one warp a token), a
-    counting sort of the (token, choice) pairs into expert order
+    How a step runs: the router's logits (and the shared expert's gate) as one product, the choice (one warp a token),
+    a counting sort of the (token, choice) pairs into expert order
     with every expert's stretch padded to whole row tiles, two grouped products over that order (the first gathers
     the tokens' rows and applies the activation), and one kernel that brings the weighted outputs back to the
     tokens and adds the shared expert.  All sizes on the host are upper bounds, so nothing is read back and the
@@ -30,28 +38,46 @@ class RoutedExperts(FeedForward):
 
     def __init__(self, runtime=None, prefix="", *, width: int, inner: int, experts: int, top: int,
                  activation: str = "relu_squared", shared_inner: int | None = None, router_bias: bool = True,
-                 init_std: float = 0.02, router_std: float = 0.5):
+                 init_std: float = 0.02, router_std: float = 0.5, gated: bool = False,
+                 rule: str = "softmax_of_chosen", weight_scale: float = 1.0, identity: int = 0,
+                 bias_name: str = "router.b", shared: PartSpec | None = None):
         super().__init__(runtime, prefix)
         self.width, self.inner, self.E, self.K = int(width), int(inner), int(experts), int(top)
-        if not 1 <= self.K <= self.E:
-            raise ValueError(f"top = {self.K} of {self.E} experts")
-        if activation not in ops.PLAIN_ACTIVATIONS:
+        self.identity = int(identity)
+        self.outputs = self.E + self.identity            # what the router tells apart
+        if not 1 <= self.K <= self.outputs:
+            raise ValueError(f"top = {self.K} of {self.outputs} experts")
+        self.gated = bool(gated)
+        if activation not in (ops.ACTIVATIONS if self.gated else ops.PLAIN_ACTIVATIONS):
             raise ValueError(f"routed experts: activation '{activation}' is not implemented")
-        self.activation = activation
+        if rule not in ops.ROUTER_RULES:
+            raise ValueError(f"routed experts: rule '{rule}' is not one of {sorted(ops.ROUTER_RULES)}")
+        self.activation, self.rule, self.weight_scale = activation, rule, float(weight_scale)
         self.shared_inner = int(shared_inner) if shared_inner else 0
+        if self.shared_inner and shared is not None:
+            raise ValueError("routed experts: one shared expert, either of the experts' plain form or a part")
+        if self.shared_inner and self.gated:
+            raise ValueError("routed experts: beside gated experts the shared expert is a part of its own (`shared`)")
+        self.shared = build_part(shared, runtime) if shared is not None else None
         self.router_bias, self.init_std, self.router_std = bool(router_bias), init_std, router_std
+        self.bias_name = bias_name
         self.up = self.down = self.router = self.router_b = None
         self.shared_up = self.shared_down = None
+
+    def children(self):
+        return [self.shared] if self.shared is not None else []
 
     def own_tensor_specs(self):
         p, init = self.prefix, ("normal", self.init_std)
         specs = {}
         for e in range(self.E):
+            if self.gated:
+                specs[f"{p}e{e}.gate"] = TensorSpec((self.inner, self.width), init=init)
             specs[f"{p}e{e}.up"] = TensorSpec((self.inner, self.width), init=init)
             specs[f"{p}e{e}.down"] = TensorSpec((self.width, self.inner), init=init)
-        specs[p + "router"] = TensorSpec((self.E, self.width), init=("normal", self.router_std))
+        specs[p + "router"] = TensorSpec((self.outputs, self.width), init=("normal", self.router_std))
         if self.router_bias:
-            specs[p + "router.b"] = TensorSpec((self.E,), init=("normal", 0.1))
+            specs[p + self.bias_name] = TensorSpec((self.outputs,), init=("normal", 0.1))
         if self.shared_inner:
             specs[p + "shared.up"] = TensorSpec((self.shared_inner, self.width), init=init)
             specs[p + "shared.down"] = TensorSpec((self.width, self.shared_inner), init=init)
@@ -60,7 +86,11 @@ class RoutedExperts(FeedForward):
 
     def own_bind(self, tensors):
         p = self.prefix
-        self.up = torch.stack([tensors[f"{p}e{e}.up"] for e in range(self.E)]).contiguous()        # [E, inner, width]
+        if self.gated:      # gate and up rows alternate, so that the product's epilogue finds a gate beside its up
+            self.up = torch.stack([interleave_rows(tensors[f"{p}e{e}.gate"], tensors[f"{p}e{e}.up"])
+                                   for e in range(self.E)]).contiguous()                           # [E, 2 inner, width]
+        else:
+            self.up = torch.stack([tensors[f"{p}e{e}.up"] for e in range(self.E)]).contiguous()    # [E, inner, width]
         self.down = torch.stack([tensors[f"{p}e{e}.down"] for e in range(self.E)]).contiguous()    # [E, width, inner]
         # the router and the shared expert's gate are one product: the gate's row lies behind the experts' rows
         # (then rows of zeros up to a multiple of 8, so that the product's float32 rows stay 16-byte aligned)
@@ -71,7 +101,7 @@ class RoutedExperts(FeedForward):
         if have % 8:
             rows.append(torch.zeros((8 - have % 8, self.width), dtype=rows[0].dtype, device=rows[0].device))
         self.router = Linear(concat_rows(rows))
-        self.router_b = tensors[p + "router.b"].to(rows[0].dtype).contiguous() if self.router_bias else None
+        self.router_b = tensors[p + self.bias_name].to(rows[0].dtype).contiguous() if self.router_bias else None
         if self.shared_inner:
             self.shared_up = Linear(tensors[p + "shared.up"])
             self.shared_down = Linear(tensors[p + "shared.down"])
@@ -86,6 +116,19 @@ class RoutedExperts(FeedForward):
     def weight_bytes(self) -> int:
         per_expert = (self.up[0].numel() + self.down[0].numel()) * self.up.element_size()
         return super().weight_bytes() + self.K * per_expert         # one token's worth; a batch reads more experts
+
+    def _shared_part(self, ctx, h, n):
+        """The shared part's output: added to the stream by its own last product where that can be (None, 0, 0), else
+        float32 shares in a buffer of its own (first share, how many, their stride)."""
+        kept = (ctx.delta_slabs, ctx.delta, ctx.pending_slabs)
+        sh = ctx.ws.alloc((ctx.max_slabs, n, self.width), torch.float32)
+        ctx.delta_slabs, ctx.delta, ctx.pending_slabs = sh, sh[0], 1
+        try:
+            self.shared.forward(ctx, h, sh[0])
+            parts = ctx.pending_slabs
+        finally:
+            ctx.delta_slabs, ctx.delta, ctx.pending_slabs = kept
+        return (None, 1, 0) if parts == 0 else (sh[0], parts, sh.stride(0))
 
     def forward(self, ctx, h, out):
         n = ctx.n_tokens
@@ -103,14 +146,19 @@ class RoutedExperts(FeedForward):
             gate = ctx.ws.alloc((n,), torch.float32) if self.shared_inner else None
             z = ctx.ws.alloc((ctx.max_slabs, n, self.router.out_features), torch.float32)
             parts = self.router.slabs(ctx, h[:n], z)
-            ops.moe_choose(z[0], self.router_b, E if self.shared_inner else -1, E, K, chosen, share, gate,
-                           n_partials=parts, partial_stride=z.stride(0))
+            ops.moe_choose(z[0], self.router_b, self.outputs if self.shared_inner else -1, self.outputs, K, chosen,
+                           share, gate, n_partials=parts, partial_stride=z.stride(0), rule=self.rule,
+                           weight_scale=self.weight_scale)
             place_token = ctx.ws.alloc((rows,), torch.int32)
             pair_place = ctx.ws.alloc((pairs,), torch.int32)
             tile_expert = ctx.ws.alloc((max_tiles,), torch.int32)
+            # (a choice beyond the experts that have weights gets no place: the combine hands the token's input on)
             ops.moe_sort(chosen, E, tile, place_token, pair_place, tile_expert)
             act = ctx.ws.alloc((rows, self.inner), rt.dtype)
-            ops.grouped_linear(h[:n], place_token, self.up, tile_expert, tile, act, self.activation, ctx)
+            if self.gated:
+                ops.grouped_gated_linear(h[:n], place_token, self.up, tile_expert, tile, act, self.activation, ctx)
+            else:
+                ops.grouped_linear(h[:n], place_token, self.up, tile_expert, tile, act, self.activation, ctx)
             y = ctx.ws.alloc((rows, D), torch.float32)
             ops.grouped_linear(act, None, self.down, tile_expert, tile, y, None, ctx)
             shared, shared_parts, shared_stride = None, 1, 0
@@ -122,7 +170,10 @@ class RoutedExperts(FeedForward):
                 sh = ctx.ws.alloc((ctx.max_slabs, n, D), torch.float32)
                 shared_parts = self.shared_down.slabs(ctx, a, sh)
                 shared, shared_stride = sh[0], sh.stride(0)
-            ops.moe_combine(y, pair_place, share, shared, shared_parts, shared_stride, gate, out, n)
+            elif self.shared is not None:
+                shared, shared_parts, shared_stride = self._shared_part(ctx, h, n)
+            ops.moe_combine(y, pair_place, share, shared, shared_parts, shared_stride, gate, out, n,
+                            pass_on=h[:n] if self.identity else None)
         ctx.pending_slabs = 1
 
 

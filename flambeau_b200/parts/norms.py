@@ -1,4 +1,4 @@
-"""RMSNorm with the residual add fused in front of it."""
+"""Norms with the residual add fused in front of them: RMSNorm, and a LayerNorm without bias."""
 from __future__ import annotations
 
 from ..kernels import ops
@@ -52,4 +52,39 @@ class RMSNorm(Norm):
         ops.add_rms_norm(x, None, self.weight, self.eps, out, n_rows=x.shape[0], weight_offset=self.weight_offset)
 
 
+class LayerNorm(Norm):
+    """y = (v - mean v) / sqrt(mean (v - mean v)^2 + eps) * w with v = x + delta: a norm that takes the mean off, with
+    a weight and no bias.  Mean, variance (from the deviations) and the product are float32; the stream stays
+    float32.  The tensor is `<prefix><weight_name>`."""
+    graph_safe = True
+
+    def __init__(self, runtime=None, prefix="", *, width: int, eps: float, init=("one_plus_normal", 0.02),
+                 weight_name: str = "weight"):
+        super().__init__(runtime, prefix)
+        self.width, self.eps, self.init, self.weight_name = int(width), float(eps), tuple(init), weight_name
+        self.weight = None
+
+    def own_tensor_specs(self):
+        return {self.prefix + self.weight_name: TensorSpec((self.width,), init=self.init)}
+
+    def own_bind(self, tensors):
+        self.weight = tensors[self.prefix + self.weight_name]
+
+    def own_weights(self):
+        return [self.weight]
+
+    def add_norm(self, ctx, x, delta, out, rows=None, n_partials: int = 1, delta_norm=None):
+        if delta_norm is not None:
+            raise ValueError("the centring norm adds a part's output as it is; a norm behind the part is not fused here")
+        if n_partials == 0 or delta is None:     # the stream already holds the sum
+            delta = None
+        stride = ctx.delta_slabs.stride(0) if n_partials > 1 else 0
+        ops.add_layer_norm(x, delta, self.weight, self.eps, out, rows=rows, n_partials=n_partials,
+                           n_rows=ctx.n_tokens, partial_stride=stride)
+
+    def normalize(self, ctx, x, out):
+        ops.add_layer_norm(x, None, self.weight, self.eps, out, n_rows=x.shape[0])
+
+
 register_part("norm", "rmsnorm", RMSNorm)
+register_part("norm", "layernorm", LayerNorm)

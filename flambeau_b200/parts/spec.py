@@ -27,11 +27,14 @@ class TensorSpec:
     ('one_plus_normal', std) or ('ones',).
     alias_of: full name of another tensor that stands for this one when the
     file does not have it (tied embeddings).
+    free_axes: axes whose size the weight file decides (a size that no configuration key gives); `shape` holds what
+    the random-weights mode draws there, and the part reads the real size from the tensor it is bound to.
     """
     shape: tuple
     kind: str = "float"
     init: tuple = ("normal", 0.02)
     alias_of: Optional[str] = None
+    free_axes: tuple = ()
 
 
 @dataclass(frozen=True)

@@ -53,7 +53,9 @@ class FolderTensors:
         for name, src in self.source.items():
             ts = specs[name]
             shape, dt = files.shape(src), files.dtype(src)
-            if tuple(shape) != tuple(ts.shape):
+            fits = len(shape) == len(ts.shape) and all(a == b or i in ts.free_axes
+                                                       for i, (a, b) in enumerate(zip(shape, ts.shape)))
+            if not fits:
                 wrong.append(f"{src}: shape {list(shape)}, wanted {list(ts.shape)}")
             elif ts.kind == "float" and not dt.is_floating_point:
                 wrong.append(f"{src}: stored as {dt}, wanted a floating type")

@@ -5,7 +5,8 @@ for shapes too large to be worth a file.
 Each tensor is drawn from a generator seeded with (seed, tensor name), so the
 values do not depend on the order of generation or on which other tensors
 exist.  Linear maps and embeddings are N(0, std); norm weights are
-1 + N(0, std) or ones, as their TensorSpec says.
+1 + N(0, std) or ones, as their TensorSpec says (and the weights of a mean over depth N(0, std) with one added to
+the newest entry's).
 """
 from __future__ import annotations
 
@@ -39,6 +40,9 @@ def draw(spec, seed: int, name: str, device="cpu") -> torch.Tensor:
         return noise
     if kind == "one_plus_normal":
         return 1.0 + noise
+    if kind == "depth_mix":                   # a mix over depth: about one for the newest entry, small for the others
+        noise[..., -1] += 1.0
+        return noise
     raise ValueError(f"tensor '{name}': unknown init rule {spec.init!r}")
 
 
