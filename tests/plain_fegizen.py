@@ -134,7 +134,7 @@ def latent_attention(h, w, p, m, eps, positions, latent=None):
     """Returns (output [n, D], (c, kr)).  `latent`: another layer's (c, kr) to read instead of forming one's own."""
     n = h.shape[0]
     H, d, r, e = m["heads"], m["dim"], m["rot_dim"], m["vdim"]
-    Rc, W = m["kv_rank"], m["mask"]["size"]
+    Rc, W = m["kv_rank"], (m["mask"]["size"] if m.get("mask") else n)
     hk = kept(h)
     cq = kept(unit_rms(hk @ w[p + "dq"].T, eps) * w[p + "dq.norm"])
     q = (cq @ w[p + "uq"].T).reshape(n, H, d + r)
@@ -232,7 +232,9 @@ def forward(cfg: dict, w: dict, tokens, collect=None, skip_mixers=()):
     latents = {}
     for i, layer in enumerate(cfg["layers"]):
         p, m = f"l{i}.", layer["mixer"]
-        h = add_time_conv(centred_norm(x, w[p + "norm1"], eps), w[p + "canon1"])
+        h = centred_norm(x, w[p + "norm1"], eps)
+        if p + "canon1" in w:
+            h = add_time_conv(h, w[p + "canon1"])
         if layer["type"] == "latent_attention":
             src = m.get("kv_from")
             y, latents[i] = latent_attention(h, w, p + "mix.", m, eps, positions,
@@ -245,13 +247,25 @@ def forward(cfg: dict, w: dict, tokens, collect=None, skip_mixers=()):
             x = x + y
         mlp = layer.get("mlp")
         if mlp is not None:
-            h = add_time_conv(centred_norm(x, w[p + "norm2"], eps), w[p + "canon2"])
+            h = centred_norm(x, w[p + "norm2"], eps)
+            if p + "canon2" in w:
+                h = add_time_conv(h, w[p + "canon2"])
             x = x + (gated_ff(h, w, p + "mlp.", gelu_tanh) if mlp["kind"] == "dense" else routed_ff(h, w, p + "mlp.", mlp))
         history.append(x)
         x = sum(w[p + "dwa"][j] * history[j] for j in range(i + 2))
         if collect is not None:
             collect.append(x.clone())
     return kept(centred_norm(x, w["final.norm"], eps)) @ w["head"].T * cfg.get("logit_scale", 1.0)
+
+
+def rounding_noise(cfg, w, tokens, dtype=torch.bfloat16):
+    """Per position, the largest difference between the logits with the 16-bit values rounded and the exact ones, as a
+    fraction of the largest exact logit: (the largest over the positions, their median)."""
+    exact = forward(cfg, w, tokens)
+    with rounding_to(dtype):
+        rounded = forward(cfg, w, tokens)
+    per_row = (rounded - exact).abs().max(dim=1).values / exact.abs().max()
+    return float(per_row.max()), float(per_row.median())
 
 
 # ---- reading a model folder -------------------------------------------------------------------------------------
