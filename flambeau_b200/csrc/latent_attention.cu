@@ -20,10 +20,20 @@
 // Rotation pairs neighbours: (x[2i], x[2i+1]) -> (x[2i] cos - x[2i+1] sin, x[2i+1] cos + x[2i] sin), i < half, with
 // per-token tables; dimensions from 2 half on pass unchanged.
 #include "common.cuh"
+#include "attention_common.cuh"
 
 __device__ __forceinline__ float mla_slab_sum(const float* row, int c, int n_partials, long partial_stride) {
+    // (the shares are fetched eight at a time before any is added, so that their latencies overlap; the order of the
+    // additions is the plain one)
     float v = row[c];
-    for (int p = 1; p < n_partials; ++p) v += row[(size_t)p * partial_stride + c];
+    for (int p0 = 1; p0 < n_partials; p0 += 8) {
+        float t[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) t[u] = p0 + u < n_partials ? row[(size_t)(p0 + u) * partial_stride + c] : 0.0f;
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            if (p0 + u < n_partials) v += t[u];
+    }
     return v;
 }
 
@@ -177,6 +187,176 @@ head_linear_kernel(const TA* __restrict__ a, long a_stride, long a_head, int n_p
     }
 }
 
+// The same map on the tensor cores, for bfloat16 weights and outputs: a CTA of four warps takes 64 tokens x 64
+// outputs of one head, every warp 16 tokens (mma.sync m16n8k16, float32 accumulation).  Inputs that come as float32
+// shares are added in float32 and rounded once to bfloat16 on their way into shared memory.  Rows of both tiles lie
+// 72 numbers apart, so that the eight rows a fragment load touches fall into different banks.
+constexpr int HM_TM = 64, HM_TN = 64, HM_KC = 64, HM_LD = HM_KC + 8;
+
+template <typename TA>
+__global__ void __launch_bounds__(128)
+head_linear_mma_kernel(const TA* __restrict__ a, long a_stride, long a_head, int n_partials, long partial_stride,
+                       const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out, long o_stride, long o_head,
+                       const float* __restrict__ gate, long gate_stride, int gate_partials, long gate_partial_stride,
+                       int gate_off, const float* __restrict__ cos_t, const float* __restrict__ sin_t, int half, int r,
+                       int n, int N, int K, int a_vec, int w_vec) {
+    fb_pdl_launch_dependents();
+    fb_pdl_wait();
+    __shared__ __align__(16) __nv_bfloat16 As[HM_TM][HM_LD];
+    __shared__ __align__(16) __nv_bfloat16 Ws[HM_TN][HM_LD];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int m0 = blockIdx.x * HM_TM, n0 = blockIdx.y * HM_TN, h = blockIdx.z;
+    const TA* ah = a + (size_t)h * a_head;
+    const __nv_bfloat16* wh = w + (size_t)h * N * K;
+    float acc[HM_TN / 8][4];
+#pragma unroll
+    for (int j = 0; j < HM_TN / 8; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[j][i] = 0.0f;
+    for (int k0 = 0; k0 < K; k0 += HM_KC) {
+        // Both tiles' loads are issued before anything is stored, so that a thread has all of them in flight at once.
+        constexpr int PER = 16 / sizeof(TA);           // numbers in 16 bytes
+        constexpr int A_GROUPS = HM_TM * (HM_KC / PER) / 128, W_GROUPS = HM_TN * (HM_KC / 8) / 128;
+        uint4 wraw[W_GROUPS];
+        if (w_vec) {
+#pragma unroll
+            for (int u = 0; u < W_GROUPS; ++u) {
+                const int idx = tid + 128 * u, nn = idx / (HM_KC / 8), k = (idx - nn * (HM_KC / 8)) * 8;
+                wraw[u] = make_uint4(0u, 0u, 0u, 0u);
+                if (n0 + nn < N && k0 + k < K) wraw[u] = *reinterpret_cast<const uint4*>(wh + (size_t)(n0 + nn) * K + k0 + k);
+            }
+        }
+        if (a_vec) {                                   // (uniform) rows and heads start on 16-byte borders, K % 8 == 0
+            float v[A_GROUPS][PER];
+            if (n_partials == 1) {
+                uint4 raw[A_GROUPS];
+#pragma unroll
+                for (int u = 0; u < A_GROUPS; ++u) {
+                    const int idx = tid + 128 * u, m = idx / (HM_KC / PER), k = (idx - m * (HM_KC / PER)) * PER;
+                    raw[u] = make_uint4(0u, 0u, 0u, 0u);       // (all bits clear is zero in both types)
+                    if (m0 + m < n && k0 + k < K)
+                        raw[u] = *reinterpret_cast<const uint4*>(ah + (size_t)(m0 + m) * a_stride + k0 + k);
+                }
+#pragma unroll
+                for (int u = 0; u < A_GROUPS; ++u) {
+                    const TA* x = reinterpret_cast<const TA*>(&raw[u]);
+#pragma unroll
+                    for (int e = 0; e < PER; ++e) v[u][e] = fb_to_float(x[e]);
+                }
+            } else {
+                // shares (few rows as a rule): per group up to eight shares in flight, added in their order
+#pragma unroll
+                for (int u = 0; u < A_GROUPS; ++u) {
+                    const int idx = tid + 128 * u, m = idx / (HM_KC / PER), k = (idx - m * (HM_KC / PER)) * PER;
+#pragma unroll
+                    for (int e = 0; e < PER; ++e) v[u][e] = 0.0f;
+                    if (m0 + m >= n || k0 + k >= K) continue;
+                    const TA* p = ah + (size_t)(m0 + m) * a_stride + k0 + k;
+                    for (int q0 = 0; q0 < n_partials; q0 += 8) {
+                        uint4 raw[8];
+#pragma unroll
+                        for (int q = 0; q < 8; ++q)
+                            raw[q] = q0 + q < n_partials ? *reinterpret_cast<const uint4*>(p + (size_t)(q0 + q) * partial_stride)
+                                                         : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) {
+                            const TA* x = reinterpret_cast<const TA*>(&raw[q]);
+                            if (q0 + q < n_partials) {
+#pragma unroll
+                                for (int e = 0; e < PER; ++e) v[u][e] += fb_to_float(x[e]);
+                            }
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < A_GROUPS; ++u) {
+                const int idx = tid + 128 * u, m = idx / (HM_KC / PER), k = (idx - m * (HM_KC / PER)) * PER;
+#pragma unroll
+                for (int e = 0; e < PER; e += 2)
+                    *reinterpret_cast<uint32_t*>(&As[m][k + e]) = fb_attn::pack_bf16(v[u][e], v[u][e + 1]);
+            }
+        } else {
+            for (int idx = tid; idx < HM_TM * HM_KC; idx += 128) {
+                const int m = idx / HM_KC, k = idx - m * HM_KC;
+                float v = 0.0f;
+                if (m0 + m < n && k0 + k < K) {
+                    const TA* p = ah + (size_t)(m0 + m) * a_stride + k0 + k;
+                    v = fb_to_float(p[0]);
+                    for (int q = 1; q < n_partials; ++q) v += fb_to_float(p[(size_t)q * partial_stride]);
+                }
+                As[m][k] = __float2bfloat16(v);
+            }
+        }
+        // the head's weights
+        if (w_vec) {
+#pragma unroll
+            for (int u = 0; u < W_GROUPS; ++u) {
+                const int idx = tid + 128 * u, nn = idx / (HM_KC / 8), k = (idx - nn * (HM_KC / 8)) * 8;
+                *reinterpret_cast<uint4*>(&Ws[nn][k]) = wraw[u];
+            }
+        } else {
+            for (int idx = tid; idx < HM_TN * HM_KC; idx += 128) {
+                const int nn = idx / HM_KC, k = idx - nn * HM_KC;
+                Ws[nn][k] = (n0 + nn < N && k0 + k < K) ? wh[(size_t)(n0 + nn) * K + k0 + k] : __float2bfloat16(0.0f);
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < HM_KC; kk += 16) {
+            uint32_t af[4];
+            af[0] = *reinterpret_cast<const uint32_t*>(&As[warp * 16 + g][kk + 2 * t]);
+            af[1] = *reinterpret_cast<const uint32_t*>(&As[warp * 16 + g + 8][kk + 2 * t]);
+            af[2] = *reinterpret_cast<const uint32_t*>(&As[warp * 16 + g][kk + 8 + 2 * t]);
+            af[3] = *reinterpret_cast<const uint32_t*>(&As[warp * 16 + g + 8][kk + 8 + 2 * t]);
+#pragma unroll
+            for (int j = 0; j < HM_TN / 8; ++j) {
+                const uint32_t b0 = *reinterpret_cast<const uint32_t*>(&Ws[j * 8 + g][kk + 2 * t]);
+                const uint32_t b1 = *reinterpret_cast<const uint32_t*>(&Ws[j * 8 + g][kk + 8 + 2 * t]);
+                fb_attn::mma_bf16(acc[j], af, b0, b1);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int j = 0; j < HM_TN / 8; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int m = m0 + warp * 16 + g + (i >> 1) * 8, c = n0 + j * 8 + 2 * t + (i & 1);
+            if (m >= n || c >= N) continue;
+            float v = acc[j][i];
+            if (gate) {
+                const float gt = mla_slab_sum(gate + (size_t)m * gate_stride, gate_off + h * N + c, gate_partials,
+                                              gate_partial_stride);
+                v = v / (1.0f + expf(-gt));
+            }
+            out[(size_t)m * o_stride + (size_t)h * o_head + c] = __float2bfloat16(v);
+        }
+    if (r > 0 && blockIdx.y == 0) {
+        // the rotated tail: columns K .. K+r of the input row go, turned, to columns N .. N+r of the output row
+        const int per = r - half;
+        for (int e = tid; e < HM_TM * per; e += 128) {
+            const int mm = e / per, i = e - mm * per, m = m0 + mm;
+            if (m >= n) break;
+            const TA* src = ah + (size_t)m * a_stride + K;
+            __nv_bfloat16* dst = out + (size_t)m * o_stride + (size_t)h * o_head + N;
+            auto in = [&](int c) {
+                float v = fb_to_float(src[c]);
+                for (int q = 1; q < n_partials; ++q) v += fb_to_float(src[(size_t)q * partial_stride + c]);
+                return v;
+            };
+            if (i < half) {
+                const float u = in(2 * i), v = in(2 * i + 1);
+                const float c = cos_t[(size_t)m * half + i], s = sin_t[(size_t)m * half + i];
+                dst[2 * i] = __float2bfloat16(u * c - v * s);
+                dst[2 * i + 1] = __float2bfloat16(v * c + u * s);
+            } else {
+                dst[half + i] = __float2bfloat16(in(half + i));
+            }
+        }
+    }
+}
+
 // proj: float32 shares [n, >= max(Rq, kv_off + Rc + r)].  cq: [n, Rq] in the engine's dtype.  With `pool` the token's
 // cache row is written as well ([pages][1][page size][Rc + r], engine dtype); without it only the query's latent.
 FB_API int fb_mla_latents(const float* proj, long long proj_stride, int n_partials, long long partial_stride, int Rq,
@@ -213,6 +393,20 @@ FB_API int fb_head_linear(const void* a, int a_dtype, long long a_stride, long l
     if (n == 0) return 0;
     if (n_partials < 1) n_partials = 1;
     if (gate_partials < 1) gate_partials = 1;
+    if (w_dtype == FB_BF16 && out_dtype == FB_BF16) {
+        // 16-byte loads where every row, head and share starts on such a border
+        const int per = a_dtype == FB_F32 ? 4 : 8;
+        const int a_vec = K % 8 == 0 && a_stride % per == 0 && a_head % per == 0 && partial_stride % per == 0 &&
+                          (uintptr_t)a % 16 == 0;
+        const int w_vec = K % 8 == 0 && (uintptr_t)w % 16 == 0;
+        const dim3 tiles((n + HM_TM - 1) / HM_TM, (N + HM_TN - 1) / HM_TN, H);
+        FB_DISPATCH_DTYPE(a_dtype, TA,
+            (fb_launch((head_linear_mma_kernel<TA>), tiles, dim3(128), 0, stream, (const TA*)a, (long)a_stride,
+                       (long)a_head, n_partials, (long)partial_stride, (const __nv_bfloat16*)w, (__nv_bfloat16*)out,
+                       (long)o_stride, (long)o_head, gate, (long)gate_stride, gate_partials, (long)gate_partial_stride,
+                       gate_off, cos_t, sin_t, half, r, n, N, K, a_vec, w_vec)));
+        return fb_check_launch("head_linear");
+    }
     const dim3 grid((n + HL_TM - 1) / HL_TM, (N + HL_TN - 1) / HL_TN, H);
     FB_DISPATCH_DTYPE(a_dtype, TA, FB_DISPATCH_DTYPE(w_dtype, TW, FB_DISPATCH_DTYPE(out_dtype, TO,
         (fb_launch((head_linear_kernel<TA, TW, TO>), grid, dim3(256), 0, stream, (const TA*)a, (long)a_stride,

@@ -14,9 +14,9 @@
 // The tail kernel runs after the convolution has read the old tail (stream order).
 #include "common.cuh"
 
-template <typename TW, typename TO>
+template <typename TO>
 __global__ void __launch_bounds__(256)
-time_conv_kernel(const float* __restrict__ h, const TW* __restrict__ w, int taps, const float* __restrict__ state,
+time_conv_kernel(const float* __restrict__ h, const float* __restrict__ wt, int taps, const float* __restrict__ state,
                  long state_stride, long tail_off, const int* __restrict__ row_seq,
                  const int* __restrict__ seq_q_start, const int* __restrict__ seq_slot, TO* __restrict__ out, int D) {
     fb_pdl_launch_dependents();
@@ -32,16 +32,16 @@ time_conv_kernel(const float* __restrict__ h, const TW* __restrict__ w, int taps
         const int back = taps - 1 - j;
         const float x = i - back >= 0 ? h[(size_t)(row - back) * D + c]
                                       : tail[(size_t)(taps - 1 + i - back) * D + c];
-        acc = fmaf(fb_to_float(w[(size_t)c * taps + j]), x, acc);
+        acc = fmaf(wt[(size_t)j * D + c], x, acc);
     }
     out[(size_t)row * D + c] = fb_from_float<TO>(acc);
 }
 
-// Four neighbouring channels a thread (D, the slots' stride and the tail's place multiples of 4): rows and tails move as
-// 16-byte vectors, so that a thread has four times the bytes in flight.
-template <typename TW, typename TO>
+// Four neighbouring channels a thread (D, the slots' stride and the tail's place multiples of 4): rows, tails and the
+// weights of a tap move as 16-byte vectors, so that a thread has four times the bytes in flight.
+template <typename TO>
 __global__ void __launch_bounds__(256)
-time_conv4_kernel(const float* __restrict__ h, const TW* __restrict__ w, int taps, const float* __restrict__ state,
+time_conv4_kernel(const float* __restrict__ h, const float* __restrict__ wt, int taps, const float* __restrict__ state,
                   long state_stride, long tail_off, const int* __restrict__ row_seq,
                   const int* __restrict__ seq_q_start, const int* __restrict__ seq_slot, TO* __restrict__ out, int D) {
     fb_pdl_launch_dependents();
@@ -52,17 +52,17 @@ time_conv4_kernel(const float* __restrict__ h, const TW* __restrict__ w, int tap
     const int seq = row_seq[row];
     const int i = row - seq_q_start[seq];
     const float* tail = state + (size_t)seq_slot[seq] * state_stride + tail_off;
-    const TW* wc = w + (size_t)c * taps;               // channel c + q's weight for tap j at wc[q * taps + j]
     float4 acc = *reinterpret_cast<const float4*>(h + (size_t)row * D + c);
     for (int j = 0; j < taps; ++j) {
         const int back = taps - 1 - j;
         const float* src = i - back >= 0 ? h + (size_t)(row - back) * D + c
                                          : tail + (size_t)(taps - 1 + i - back) * D + c;
         const float4 x = *reinterpret_cast<const float4*>(src);
-        acc.x = fmaf(fb_to_float(wc[j]), x.x, acc.x);
-        acc.y = fmaf(fb_to_float(wc[taps + j]), x.y, acc.y);
-        acc.z = fmaf(fb_to_float(wc[2 * taps + j]), x.z, acc.z);
-        acc.w = fmaf(fb_to_float(wc[3 * taps + j]), x.w, acc.w);
+        const float4 wj = *reinterpret_cast<const float4*>(wt + (size_t)j * D + c);
+        acc.x = fmaf(wj.x, x.x, acc.x);
+        acc.y = fmaf(wj.y, x.y, acc.y);
+        acc.z = fmaf(wj.z, x.z, acc.z);
+        acc.w = fmaf(wj.w, x.w, acc.w);
     }
     TO* o = out + (size_t)row * D + c;
     o[0] = fb_from_float<TO>(acc.x);
@@ -89,8 +89,9 @@ time_conv_tail_kernel(const float* __restrict__ h, int taps, float* __restrict__
     }
 }
 
-// h: float32 [n, D] contiguous; w: [D, taps]; out: [n, D] contiguous in the engine's dtype.
-FB_API int fb_time_conv(const float* h, const void* w, int w_dtype, int taps, float* state, long long state_stride,
+// h: float32 [n, D] contiguous; wt: float32 [taps, D], tap by tap (a warp reads neighbouring channels' weights of one
+// tap side by side); out: [n, D] contiguous in the engine's dtype.
+FB_API int fb_time_conv(const float* h, const float* wt, int taps, float* state, long long state_stride,
                         long long tail_off, const int* row_seq, const int* seq_q_start, const int* seq_q_len,
                         const int* seq_slot, int n_seqs, void* out, int out_dtype, int n, int D, cudaStream_t stream) {
     FB_REQUIRE(n >= 0 && D > 0 && taps >= 1 && n_seqs >= 0, "time_conv: bad sizes");
@@ -99,16 +100,16 @@ FB_API int fb_time_conv(const float* h, const void* w, int w_dtype, int taps, fl
     const unsigned stretches = (unsigned)((D + 255) / 256);
     FB_REQUIRE(stretches <= 65535, "time_conv: width %d is too large", D);
     const bool by4 = D % 4 == 0 && state_stride % 4 == 0 && tail_off % 4 == 0 && (uintptr_t)h % 16 == 0 &&
-                     (!state || (uintptr_t)state % 16 == 0);
+                     (uintptr_t)wt % 16 == 0 && (!state || (uintptr_t)state % 16 == 0);
     if (by4) {
         const unsigned stretches4 = (unsigned)((D / 4 + 255) / 256);
-        FB_DISPATCH_DTYPE(w_dtype, TW, FB_DISPATCH_DTYPE(out_dtype, TO,
-            (fb_launch((time_conv4_kernel<TW, TO>), dim3(n, stretches4), dim3(256), 0, stream, h, (const TW*)w, taps,
-                       (const float*)state, (long)state_stride, (long)tail_off, row_seq, seq_q_start, seq_slot, (TO*)out, D))));
+        FB_DISPATCH_DTYPE(out_dtype, TO,
+            (fb_launch((time_conv4_kernel<TO>), dim3(n, stretches4), dim3(256), 0, stream, h, wt, taps,
+                       (const float*)state, (long)state_stride, (long)tail_off, row_seq, seq_q_start, seq_slot, (TO*)out, D)));
     } else {
-        FB_DISPATCH_DTYPE(w_dtype, TW, FB_DISPATCH_DTYPE(out_dtype, TO,
-            (fb_launch((time_conv_kernel<TW, TO>), dim3(n, stretches), dim3(256), 0, stream, h, (const TW*)w, taps,
-                       (const float*)state, (long)state_stride, (long)tail_off, row_seq, seq_q_start, seq_slot, (TO*)out, D))));
+        FB_DISPATCH_DTYPE(out_dtype, TO,
+            (fb_launch((time_conv_kernel<TO>), dim3(n, stretches), dim3(256), 0, stream, h, wt, taps,
+                       (const float*)state, (long)state_stride, (long)tail_off, row_seq, seq_q_start, seq_slot, (TO*)out, D)));
     }
     int rc = fb_check_launch("time_conv");
     if (rc || taps < 2) return rc;

@@ -65,7 +65,7 @@ _SIGNATURES = {
     "fb_add_layernorm": (I, [P, P, I, L, P, I, P, I, P, I, I, F, STREAM]),
     "fb_depth_average": (I, [P, P, I, L, P, L, I, P, I, L, STREAM]),
     # time_conv.cu
-    "fb_time_conv": (I, [P, P, I, I, P, L, L, P, P, P, P, I, P, I, I, I, STREAM]),
+    "fb_time_conv": (I, [P, P, I, P, L, L, P, P, P, P, I, P, I, I, I, STREAM]),
     # linear_attention.cu
     "fb_gla_prepare": (I, [P, L, I, L, P, P, I, I, F, F, P, P, I, I, I, I, STREAM]),
     "fb_gla_recurrent": (I, [P, P, P, L, P, P, P, I, P, I, I, I, STREAM]),

@@ -1030,18 +1030,20 @@ def depth_average(x: torch.Tensor, delta, n_partials: int, partial_stride: int, 
           "depth_average")
 
 
-def time_conv(h: torch.Tensor, w: torch.Tensor, state, tail_off: int, batch, out: torch.Tensor, n: int) -> None:
-    """out[t] = h[t] + sum_j w[:, j] * h[t - taps + 1 + j] per request (csrc/time_conv.cu); h float32 [n, D]; w
-    [D, taps]; state float32 [slots, floats] with the kept inputs [taps - 1, D] at tail_off, updated for the next step."""
-    _cuda(h, w, state, out)
-    D, taps = w.shape
+def time_conv(h: torch.Tensor, wt: torch.Tensor, state, tail_off: int, batch, out: torch.Tensor, n: int) -> None:
+    """out[t] = h[t] + sum_j wt[j] * h[t - taps + 1 + j] per request (csrc/time_conv.cu); h float32 [n, D]; wt float32
+    [taps, D] (the weights tap by tap); state float32 [slots, floats] with the kept inputs [taps - 1, D] at tail_off,
+    updated for the next step."""
+    _cuda(h, wt, state, out)
+    taps, D = wt.shape
     if h.dtype != torch.float32 or not h.is_contiguous() or h.shape[1] != D or not out.is_contiguous() \
-            or out.shape[1] != D or out.shape[0] < n or h.shape[0] < n or not w.is_contiguous():
+            or out.shape[1] != D or out.shape[0] < n or h.shape[0] < n or not wt.is_contiguous() \
+            or wt.dtype != torch.float32:
         raise KernelError("time_conv: bad shapes")
     if taps > 1 and (state is None or state.dtype != torch.float32 or state.dim() != 2 or not state.is_contiguous()
                      or state.shape[1] < tail_off + (taps - 1) * D):
         raise KernelError("time_conv: the state slot is too small for the kept inputs")
-    check(lib().fb_time_conv(h.data_ptr(), w.data_ptr(), dtype_code(w), int(taps), _ptr(state),
+    check(lib().fb_time_conv(h.data_ptr(), wt.data_ptr(), int(taps), _ptr(state),
                              state.stride(0) if state is not None else 0, int(tail_off), batch.row_seq.data_ptr(),
                              batch.seq_q_start_d.data_ptr(), batch.seq_q_len_d.data_ptr(), batch.seq_slot_d.data_ptr(),
                              batch.n_seqs, out.data_ptr(), dtype_code(out), int(n), D, _stream()), "time_conv")

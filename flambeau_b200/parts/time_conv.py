@@ -22,7 +22,7 @@ class TimeConvResidual(Part):
         if self.taps < 1:
             raise ValueError("a convolution over time needs at least one tap")
         self.init_std = float(init_std) if init_std is not None else 0.5 / self.taps ** 0.5
-        self.weight = None
+        self.weight = self.weight_t = None
 
     def state_floats(self) -> int:
         return (self.taps - 1) * self.width
@@ -32,6 +32,8 @@ class TimeConvResidual(Part):
 
     def own_bind(self, tensors):
         self.weight = tensors[self.prefix + self.weight_name].contiguous()
+        # tap by tap in float32 (exact), so that neighbouring channels' weights of one tap lie side by side
+        self.weight_t = self.weight.t().float().contiguous()
 
     def own_weights(self):
         return [self.weight]
@@ -39,7 +41,7 @@ class TimeConvResidual(Part):
     def forward(self, ctx, h, out, state, offset: int) -> None:
         """h: float32 [n, width] normalised rows; out: [n, width] engine dtype; state: float32 [slots, floats] whose
         numbers from `offset` on are this part's."""
-        ops.time_conv(h, self.weight, state, offset, ctx.batch, out, ctx.n_tokens)
+        ops.time_conv(h, self.weight_t, state, offset, ctx.batch, out, ctx.n_tokens)
 
 
 register_part("input_map", "time_conv", TimeConvResidual)

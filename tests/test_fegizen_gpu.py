@@ -61,24 +61,27 @@ def test_centring_norm_with_the_add_in_front(width, dtype):
 
 @pytest.mark.parametrize("taps", [1, 2, 4, 5])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_convolution_over_time_across_steps(taps, dtype):
+@pytest.mark.parametrize("layout", [(40, 7, 3), (72, 8, 4)], ids=["ragged", "by16bytes"])
+def test_convolution_over_time_across_steps(taps, dtype, layout):
     """Three requests in three slots, fed in steps of unequal portions (one token, two, many; portions shorter than
-    the taps follow each other), their kept inputs at an offset inside the slot; then a slot zeroed and used again."""
+    the taps follow each other), their kept inputs at an offset inside the slot; then a slot zeroed and used again.
+    Once with a width and an offset that leave nothing aligned, once with rows that move as 16-byte vectors."""
     from flambeau_b200.kernels import ops
-    D, off = 40, 7
+    D, off, pad = layout
     g = torch.Generator().manual_seed(taps)
     lengths = [23, 9, 40]
     w = (torch.randn(D, taps, generator=g) * 0.5).to(DT[dtype])
     hs = [torch.randn(L, D, generator=g) for L in lengths]
     want = [pf.add_time_conv(h.double(), w.double()) for h in hs]
-    state = torch.zeros((4, off + (taps - 1) * D + 3), dtype=torch.float32, device=DEV)
+    state = torch.zeros((4, off + (taps - 1) * D + pad), dtype=torch.float32, device=DEV)
     state[3].fill_(float("nan"))
+    wt = w.t().float().contiguous().to(DEV)            # tap by tap, as the part hands the weights to the kernel
     slots, at, got = [2, 0, 1], [0, 0, 0], [[], [], []]
     for portion in [[1, 2, 5], [1, 1, 17], [2, 0, 1], [3, 6, 16], [16, 0, 1]]:
         live = [(s, k) for s, k in enumerate(portion) if k]
         h = torch.cat([hs[s][at[s]:at[s] + k] for s, k in live]).to(DEV)
         out = torch.empty((h.shape[0], D), dtype=DT[dtype], device=DEV)
-        ops.time_conv(h, w.to(DEV), state, off, fake_batch([k for _, k in live], [slots[s] for s, _ in live]), out,
+        ops.time_conv(h, wt, state, off, fake_batch([k for _, k in live], [slots[s] for s, _ in live]), out,
                       h.shape[0])
         r = 0
         for s, k in live:
@@ -94,7 +97,7 @@ def test_convolution_over_time_across_steps(taps, dtype):
     assert bool(torch.isnan(state[3]).all()), "a slot that no sequence of the step uses was written"
     state[slots[1]].zero_()
     out = torch.empty((lengths[1], D), dtype=DT[dtype], device=DEV)
-    ops.time_conv(hs[1].to(DEV), w.to(DEV), state, off, fake_batch([lengths[1]], [slots[1]]), out, lengths[1])
+    ops.time_conv(hs[1].to(DEV), wt, state, off, fake_batch([lengths[1]], [slots[1]]), out, lengths[1])
     assert rel_err(out, want[1]) < tol
 
 
@@ -218,18 +221,20 @@ def test_latents_are_normed_turned_and_written_to_their_pages(sizes, dtype):
 
 @pytest.mark.parametrize("shape", [(3, 24, 40, 0), (4, 32, 96, 16), (20, 4, 20, 6), (1, 130, 70, 8), (2, 96, 33, 0)], ids=str)
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_a_map_per_head(shape, dtype):
+@pytest.mark.parametrize("rows", [(13, 2), (150, 1), (70, 3)], ids=str)
+def test_a_map_per_head(shape, dtype, rows):
     """out_h = W_h a_h for every head, the input as shares or as one array; behind the map either a turned tail of
-    the head that is copied along, or a sigmoid gate."""
+    the head that is copied along, or a sigmoid gate.  Few rows in two shares, several row tiles in one share, and a
+    ragged second tile in three."""
     from flambeau_b200.kernels import ops
     H, K, N, rot = shape
     dt = DT[dtype]
     g = torch.Generator().manual_seed(H * K)
-    n = 13
+    n, parts = rows
     w = (torch.randn(H, N, K, generator=g) * 0.3).to(dt)
     positions = list(range(100, 100 + n))
     freqs, mag = pf.rotary_frequencies({"base": 50.0, "dims": rot}) if rot else (None, 1.0)
-    shares = torch.randn(2, n, H * (K + rot) + 8, generator=g)
+    shares = torch.randn(parts, n, H * (K + rot) + 8, generator=g)
     a = shares.sum(0).double()[:, :H * (K + rot)].reshape(n, H, K + rot)
     want = torch.einsum("hnk,thk->thn", w.double(), a[..., :K])
     if rot:
@@ -240,18 +245,18 @@ def test_a_map_per_head(shape, dtype):
         ang = torch.tensor(positions, dtype=F64)[:, None] * freqs[None]
         cos, sin = torch.cos(ang).float().to(DEV), torch.sin(ang).float().to(DEV)
     sh = shares.to(DEV).contiguous()
-    ops.head_linear(sh[0], K + rot, w.to(DEV), out, N + rot, n, n_partials=2, partial_stride=sh.stride(0), cos=cos,
+    ops.head_linear(sh[0], K + rot, w.to(DEV), out, N + rot, n, n_partials=parts, partial_stride=sh.stride(0), cos=cos,
                     sin=sin, half=rot // 2, rot=rot)
     tol = 1e-5 if dtype == "float32" else 1.5e-2
     assert rel_err(out, want.reshape(n, -1)) < tol
     # the second use: an input in the engine's dtype, a gate that arrives as shares at an offset
-    a2 = torch.randn(n, H * (K + 4), generator=g).to(dt)
+    a2 = torch.randn(n, H * (K + 8), generator=g).to(dt)
     gate = torch.randn(2, n, 5 + H * N + 3, generator=g)
-    want = torch.einsum("hnk,thk->thn", w.double(), a2.double().reshape(n, H, K + 4)[..., :K]).reshape(n, H * N) \
+    want = torch.einsum("hnk,thk->thn", w.double(), a2.double().reshape(n, H, K + 8)[..., :K]).reshape(n, H * N) \
         * torch.sigmoid(gate.sum(0).double()[:, 5:5 + H * N])
     out = torch.empty((n, H * N), dtype=dt, device=DEV)
     gd = gate.to(DEV).contiguous()
-    ops.head_linear(a2.to(DEV), K + 4, w.to(DEV), out, N, n, gate=gd[0], gate_off=5, gate_partials=2,
+    ops.head_linear(a2.to(DEV), K + 8, w.to(DEV), out, N, n, gate=gd[0], gate_off=5, gate_partials=2,
                     gate_partial_stride=gd.stride(0))
     assert rel_err(out, want) < tol
 
