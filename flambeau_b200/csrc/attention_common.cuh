@@ -61,6 +61,9 @@ struct AttnArgs {
     int short_ctas;                    // split-key: CTAs of the split-key launch
     int min_tiles;                     // split-key: a CTA's stretch is at least this long
     int short_rows;                    // sequences with q_len * G <= short_rows belong to the split-key arrangement
+    int kv_share;                      // split-key arrangement only: this many of the `nkv` key/value heads it is given
+                                       // are one stored head (a group of more than 16 query heads is cut into
+                                       // stretches that read the same cache rows); 1 as a rule
     FbPrefetch prefetch;               // split-key: rows to fetch into L2 when a CTA has issued its last tile
     int* status;
 };

@@ -433,6 +433,16 @@ bool attention_tc_enabled() {
 
 }  // namespace
 
+// Into how many equal stretches of at most 16 heads a group of nh / nkv query heads is cut for the split-key
+// arrangement: 1 up to 16 heads, else the smallest divisor of the group that leaves at most 16.
+FB_API int fb_attention_kv_share(int nh, int nkv) {
+    const int G = nkv > 0 ? nh / nkv : 1;
+    if (G <= 16) return 1;
+    for (int s = 2; s < G; ++s)
+        if (G % s == 0 && G / s <= 16) return s;
+    return G;
+}
+
 // Portions of prompts run on the tcgen05 kernel where it takes the geometry (1, the default) or always on the
 // mma.sync kernel (0).
 FB_API void fb_set_attention_tc(int on) { g_attention_tc = on ? 1 : 0; }
@@ -480,12 +490,12 @@ FB_API int fb_paged_attention_mma(const void* q, long long q_stride, void* out, 
     a.sinks = sinks;
     a.weights_hi_lo = weights_hi_lo ? 1 : 0;
     a.status = status;
-    a.short_rows = G <= 16 ? 16 : 0;               // with more than 16 heads per group even one token is "long"
-    if (a.short_rows == 0) {                       // then single tokens run in the arrangement for portions as well,
-        any_long = any_long || any_short;          // whose grid must cover every sequence
-        any_short = 0;
-        a.multi_seqs = nullptr;
-    }
+    // The split-key arrangement holds 16 rows (tokens x query heads of a group).  A group of more than 16 heads is cut
+    // into `share` equal stretches of at most 16, each of which it takes for a key/value head of its own that reads
+    // the same cache rows (fb_attention_kv_share; the host's test of what is short uses the same number).
+    const int share = fb_attention_kv_share(nh, nkv);
+    a.kv_share = 1;
+    a.short_rows = 16 * share;                     // the arrangements for portions test q_len * G against this
     // whole pages fetched by tensor-map copies when a 64-key tile is a whole number of pages and the head a whole
     // number of 64-column blocks; single rows by bulk copies otherwise
     const bool tma = hd % 64 == 0 && page_size >= 8 && page_size <= KT && KT % page_size == 0;
@@ -506,6 +516,11 @@ FB_API int fb_paged_attention_mma(const void* q, long long q_stride, void* out, 
                            : launch_long(a, HD_MAX, tma, n_seqs, max_q_len, stream);
         if (rc) return rc;
     }
-    if (any_short) return fb_launch_attention_split(a, HD_MAX, tma, n_seqs, scratch, scratch_floats, stream);
+    if (any_short) {
+        a.nkv = nkv * share;
+        a.kv_share = share;
+        a.short_rows = 16;
+        return fb_launch_attention_split(a, HD_MAX, tma, n_seqs, scratch, scratch_floats, stream);
+    }
     return 0;
 }

@@ -294,7 +294,7 @@ attention_split_kernel(const __grid_constant__ AttnArgs a) {
                         __nv_bfloat16* dst = (is_v ? v_tile(buf) : k_tile(buf)) + cb * (KT * 64) + pj * a.page_size * 64;
                         mbar_expect_tx(bar, (uint32_t)(a.page_size * 128));
                         tma_load_2d(smem_u32(dst), is_v ? &a.map_v : &a.map_k, bar, cb * 64,
-                                    (page * a.nkv + sg.kvh) * a.page_size);
+                                    (page * (a.nkv / a.kv_share) + sg.kvh / a.kv_share) * a.page_size);
                     } else {
                         mbar_arrive(bar);             // stale (finite) data stays in the slot; it is masked
                     }
@@ -304,7 +304,8 @@ attention_split_kernel(const __grid_constant__ AttnArgs a) {
                     __nv_bfloat16* dst = (is_v ? v_tile(buf) : k_tile(buf)) + r * LDS;
                     if (page >= 0) {
                         const int t = tile_start + r;
-                        const size_t off = (((size_t)page * a.nkv + sg.kvh) * a.page_size + (t % a.page_size)) * hd;
+                        const size_t off = (((size_t)page * (a.nkv / a.kv_share) + sg.kvh / a.kv_share) * a.page_size +
+                                            (t % a.page_size)) * hd;
                         mbar_expect_tx(bar, (uint32_t)(hd * 2));
                         bulk_copy_g2s(smem_u32(dst), (is_v ? a.v_pool : a.k_pool) + off, (uint32_t)(hd * 2), bar);
                     } else {

@@ -178,6 +178,21 @@ __device__ __forceinline__ float fb_block_max(float v, float* scratch) {
     return r;
 }
 
+// One number of a product that arrives as float32 split-K shares `partial_stride` apart: the shares are fetched eight
+// at a time before any is added, so that their latencies overlap; the order of the additions is the plain one.
+__device__ __forceinline__ float fb_slab_sum(const float* row, int c, int n_partials, long partial_stride) {
+    float v = row[c];
+    for (int p0 = 1; p0 < n_partials; p0 += 8) {
+        float t[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) t[u] = p0 + u < n_partials ? row[(size_t)(p0 + u) * partial_stride + c] : 0.0f;
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            if (p0 + u < n_partials) v += t[u];
+    }
+    return v;
+}
+
 // Dispatch a dtype code to a template parameter.
 #define FB_DISPATCH_DTYPE(code, T, ...)                                   \
     do {                                                                  \

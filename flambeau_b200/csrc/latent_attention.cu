@@ -23,18 +23,7 @@
 #include "attention_common.cuh"
 
 __device__ __forceinline__ float mla_slab_sum(const float* row, int c, int n_partials, long partial_stride) {
-    // (the shares are fetched eight at a time before any is added, so that their latencies overlap; the order of the
-    // additions is the plain one)
-    float v = row[c];
-    for (int p0 = 1; p0 < n_partials; p0 += 8) {
-        float t[8];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) t[u] = p0 + u < n_partials ? row[(size_t)(p0 + u) * partial_stride + c] : 0.0f;
-#pragma unroll
-        for (int u = 0; u < 8; ++u)
-            if (p0 + u < n_partials) v += t[u];
-    }
-    return v;
+    return fb_slab_sum(row, c, n_partials, partial_stride);
 }
 
 template <typename TW, typename TO>

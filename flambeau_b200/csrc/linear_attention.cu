@@ -20,9 +20,7 @@
 #include "common.cuh"
 
 __device__ __forceinline__ float gla_slab_sum(const float* row, int c, int n_partials, long partial_stride) {
-    float v = row[c];
-    for (int p = 1; p < n_partials; ++p) v += row[(size_t)p * partial_stride + c];
-    return v;
+    return fb_slab_sum(row, c, n_partials, partial_stride);
 }
 
 template <typename TW>

@@ -28,20 +28,7 @@ moe_choose_kernel(const float* __restrict__ z_in, long z_stride, int n_partials,
     const int row = blockIdx.x * 4 + warp;
     if (row >= n) return;
     const float* zr = z_in + (size_t)row * z_stride;
-    // (the shares are fetched eight at a time before any is added, so that their latencies overlap; the order of
-    // the additions is the plain one)
-    auto logit = [&](int c) {
-        float v = zr[c];
-        for (int p0 = 1; p0 < n_partials; p0 += 8) {
-            float t[8];
-#pragma unroll
-            for (int u = 0; u < 8; ++u) t[u] = p0 + u < n_partials ? zr[(size_t)(p0 + u) * partial_stride + c] : 0.0f;
-#pragma unroll
-            for (int u = 0; u < 8; ++u)
-                if (p0 + u < n_partials) v += t[u];
-        }
-        return v;
-    };
+    auto logit = [&](int c) { return fb_slab_sum(zr, c, n_partials, partial_stride); };
     float z[MOE_MAX_LOGITS_PER_LANE];                  // lane l keeps the logits of experts l, l + 32, ...
     if (rule == 1) {
         // scores over all experts first; the bias only moves the choice

@@ -709,7 +709,7 @@ def paged_attention_mma(q, out, k_pool, v_pool, block_table, seq_q_start, seq_q_
                         weights_float32: bool = False) -> None:
     """bfloat16 attention on the tensor cores over the paged cache; sequences are described per entry of the
     step (first row, rows, first position).  any_short / any_long say whether the step holds sequences with
-    rows * (nh/nkv) <= 16 / > 16, which run in different arrangements of the kernel.  table_base (int32 per
+    rows * (nh/nkv) <= 16 / > 16 (attention_is_short), which run in different arrangements of the kernel.  table_base (int32 per
     sequence, optional): the logical page that column 0 of each table row stands for.  prefetch (optional): the
     weight matrix of the product that follows (see prefetch_arguments).  multi_seqs (int32, optional): the
     n_multi sequences of the step that bring more than one token; the kernels for portions then lay their grid over
@@ -732,7 +732,7 @@ def paged_attention_mma(q, out, k_pool, v_pool, block_table, seq_q_start, seq_q_
         raise KernelError("attention_mma: q, out and the cache must be bfloat16")
     if not k_pool.is_contiguous() or not v_pool.is_contiguous():
         raise KernelError("attention: cache pools must be contiguous")
-    scratch = _AttentionScratch.get(q.device, n_seqs, nkv, hd)
+    scratch = _AttentionScratch.get(q.device, n_seqs, nkv * attention_kv_share(nh, nkv), hd)
     check(lib().fb_paged_attention_mma(
         q.data_ptr(), _rows(q), out.data_ptr(), _rows(out), k_pool.data_ptr(), v_pool.data_ptr(), page_size, n_pages,
         block_table.data_ptr(), block_table.stride(0), _ptr(table_base), seq_q_start.data_ptr(),
@@ -743,6 +743,21 @@ def paged_attention_mma(q, out, k_pool, v_pool, block_table, seq_q_start, seq_q_
         *prefetch_arguments(prefetch), status.data_ptr(), _stream()), "paged_attention_mma")
 
 
+def attention_kv_share(nh: int, nkv: int) -> int:
+    """Into how many equal stretches of at most 16 heads the split-key arrangement cuts a group of nh / nkv query
+    heads (1 up to 16 heads; the launcher's own number, csrc/attention_mma.cu)."""
+    G = nh // nkv if nkv > 0 else 1
+    if G <= 16:
+        return 1
+    return next((s for s in range(2, G) if G % s == 0 and G // s <= 16), G)
+
+
+def attention_is_short(q_len: int, nh: int, nkv: int) -> bool:
+    """Whether a sequence that brings q_len tokens runs in the split-key arrangement of paged_attention_mma (its
+    tokens x the query heads of a stretch fit 16 rows) rather than in the arrangement for portions."""
+    return q_len * ((nh // nkv) // attention_kv_share(nh, nkv)) <= 16
+
+
 def paged_attention(ctx, q, out, cache, nh: int, nkv: int, hd: int, window: int, scale: float,
                     next_weight=None, score_slopes=None, sinks=None, vd: int = 0, weights_float32: bool = False) -> None:
     """Attention of every row of the step over its request's cached keys: the tensor-core kernel for bfloat16
@@ -751,8 +766,7 @@ def paged_attention(ctx, q, out, cache, nh: int, nkv: int, hd: int, window: int,
     b = ctx.batch
     vd = int(vd) or hd
     if mma_attention_supported(q, nh, nkv, hd) and vd == hd:
-        G = nh // nkv
-        short = [ql * G <= 16 for ql in b.seq_q_len]
+        short = [attention_is_short(ql, nh, nkv) for ql in b.seq_q_len]
         paged_attention_mma(q, out, cache.k_pool, cache.v_pool, cache.block_table, b.seq_q_start_d, b.seq_q_len_d,
                             b.seq_pos_start_d, b.n_seqs, b.max_q_len, b.max_kv_len, any(short), not all(short),
                             nh, nkv, hd, window, scale, ctx.runtime.status, table_base=cache.table_base,

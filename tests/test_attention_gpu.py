@@ -108,8 +108,7 @@ class Scene:
                                      self.nh, self.nkv, self.hd, self.window, scale, status, table_base=base,
                                      score_slopes=slopes)
         else:
-            G = self.nh // self.nkv
-            short = [n * G <= 16 for _, n in self.seqs]
+            short = [ops.attention_is_short(n, self.nh, self.nkv) for _, n in self.seqs]
             assert ops.mma_attention_supported(q, self.nh, self.nkv, self.hd)
             multi = [s for s, (_, n) in enumerate(self.seqs) if n > 1]      # as the engine's descriptor lists them
             multi_d = torch.tensor(multi + [0], dtype=torch.int32, device=dev)

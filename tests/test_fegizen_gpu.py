@@ -261,7 +261,8 @@ def test_a_map_per_head(shape, dtype, rows):
     assert rel_err(out, want) < tol
 
 
-LATENT_GEOMETRIES = [(4, 112, 136, 16), (20, 26, 1, 16), (1, 64, 500, 32), (3, 48, 20, 8), (2, 64, 40, 64), (8, 160, 33, 16)]
+LATENT_GEOMETRIES = [(4, 112, 136, 16), (20, 26, 1, 16), (1, 64, 500, 32), (3, 48, 20, 8), (2, 64, 40, 64), (8, 160, 33, 16),
+                     (32, 64, 40, 16), (24, 128, 100, 32), (17, 64, 30, 16)]   # (more than 16 heads on the one key/value head)
 
 
 @pytest.mark.parametrize("geometry", LATENT_GEOMETRIES, ids=lambda g: "h%d-row%d-w%d-p%d" % g)

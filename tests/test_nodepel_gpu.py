@@ -126,8 +126,8 @@ def test_windowed_attention_with_a_sink(geometry, dtype):
         G = nh // nkv
         starts = [sum(lens[:i]) for i in range(len(lens))]
         args = (c.k_pool, c.v_pool, c.block_table, i32(starts), i32(lens), i32([ctx for ctx, _ in seqs]), len(seqs),
-                max(lens), max(ctx + n for ctx, n in seqs), any(n * G <= 16 for n in lens),
-                any(n * G > 16 for n in lens), nh, nkv, hd, window, scale, status)
+                max(lens), max(ctx + n for ctx, n in seqs), any(ops.attention_is_short(n, nh, nkv) for n in lens),
+                any(not ops.attention_is_short(n, nh, nkv) for n in lens), nh, nkv, hd, window, scale, status)
         # the weights as two bfloat16 numbers each through P V: what is left is the rounding of the output
         exact = torch.empty_like(out)
         ops.paged_attention_mma(q_d, exact, *args, table_base=c.table_base, sinks=sink.float().to(DEV),
