@@ -64,7 +64,7 @@ template <int LEFT> __device__ __forceinline__ void gla_copies_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(LEFT) : "memory");
 }
 
-// LPC lanes a column, R state values a lane (the key channel d = lane + LPC r, dk <= LPC R), 256 / LPC columns a CTA.
+// LPC lanes a column, R state values a lane (dk <= LPC R), 256 / LPC columns a CTA.
 template <int R, int LPC> struct GlaTile {
     static constexpr int THREADS = 256, COLS = THREADS / LPC, DKP = LPC * R;
     static constexpr int CH = DKP <= 128 ? 32 : DKP <= 256 ? 16 : 8;         // tokens fetched at a time
@@ -117,10 +117,14 @@ gla_recurrent_kernel(const float* __restrict__ qkv, const float* __restrict__ de
         gla_copies_commit();
     };
 
+    // Which key channels a lane holds: four neighbouring ones out of every 4 LPC where R allows it (a lane fetches them
+    // as one 16-byte vector and neighbouring lanes read neighbouring vectors), else every LPC-th.
+    constexpr bool VEC = R % 4 == 0;
+    auto channel = [&](int r) { return VEC ? (r / 4) * (4 * LPC) + 4 * li + (r & 3) : li + LPC * r; };
     float s[R];
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-        const int d = li + LPC * r;
+        const int d = channel(r);
         s[r] = (live && d < dk) ? S[d] : 0.0f;
     }
     if (L > 0) fetch(0, sh);
@@ -136,16 +140,36 @@ gla_recurrent_kernel(const float* __restrict__ qkv, const float* __restrict__ de
         const float* ks = qs + CH * DKP;
         const float* as = ks + CH * DKP;
         const float* vs = as + CH * DKP;
+        // (four tokens unrolled: only the state's multiply-adds depend on the token before, so the loads, the sums
+        // and the exchanges between lanes of neighbouring tokens overlap)
+#pragma unroll 4
         for (int t = 0; t < cnt; ++t) {
             const float v = vs[t * COLS + tid / LPC];
-            const float* qt = qs + t * DKP + li;
-            const float* kt = ks + t * DKP + li;
-            const float* at = as + t * DKP + li;
+            float qv[R], kv[R], av[R];
+            if constexpr (VEC) {
+                const float4* q4 = reinterpret_cast<const float4*>(qs + t * DKP) + li;
+                const float4* k4 = reinterpret_cast<const float4*>(ks + t * DKP) + li;
+                const float4* a4 = reinterpret_cast<const float4*>(as + t * DKP) + li;
+#pragma unroll
+                for (int r = 0; r < R / 4; ++r) {
+                    const float4 a = q4[r * LPC], b = k4[r * LPC], c = a4[r * LPC];
+                    qv[4 * r] = a.x; qv[4 * r + 1] = a.y; qv[4 * r + 2] = a.z; qv[4 * r + 3] = a.w;
+                    kv[4 * r] = b.x; kv[4 * r + 1] = b.y; kv[4 * r + 2] = b.z; kv[4 * r + 3] = b.w;
+                    av[4 * r] = c.x; av[4 * r + 1] = c.y; av[4 * r + 2] = c.z; av[4 * r + 3] = c.w;
+                }
+            } else {
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    qv[r] = qs[t * DKP + li + LPC * r];
+                    kv[r] = ks[t * DKP + li + LPC * r];
+                    av[r] = as[t * DKP + li + LPC * r];
+                }
+            }
             float acc0 = 0.0f, acc1 = 0.0f;
 #pragma unroll
             for (int r = 0; r < R; ++r) {
-                s[r] = fmaf(at[LPC * r], s[r], kt[LPC * r] * v);
-                if (r & 1) acc1 = fmaf(s[r], qt[LPC * r], acc1); else acc0 = fmaf(s[r], qt[LPC * r], acc0);
+                s[r] = fmaf(av[r], s[r], kv[r] * v);
+                if (r & 1) acc1 = fmaf(s[r], qv[r], acc1); else acc0 = fmaf(s[r], qv[r], acc0);
             }
             float acc = acc0 + acc1;
 #pragma unroll
@@ -156,7 +180,7 @@ gla_recurrent_kernel(const float* __restrict__ qkv, const float* __restrict__ de
     }
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-        const int d = li + LPC * r;
+        const int d = channel(r);
         if (live && d < dk) S[d] = s[r];
     }
 }
