@@ -183,7 +183,7 @@ head_linear_kernel(const TA* __restrict__ a, long a_stride, long a_head, int n_p
 constexpr int HM_TM = 64, HM_TN = 64, HM_KC = 64, HM_LD = HM_KC + 8;
 
 template <typename TA>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 4)
 head_linear_mma_kernel(const TA* __restrict__ a, long a_stride, long a_head, int n_partials, long partial_stride,
                        const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out, long o_stride, long o_head,
                        const float* __restrict__ gate, long gate_stride, int gate_partials, long gate_partial_stride,
@@ -307,19 +307,43 @@ head_linear_mma_kernel(const TA* __restrict__ a, long a_stride, long a_head, int
         }
         __syncthreads();
     }
+    // An accumulator pair (two neighbouring outputs of a row) leaves as one 4-byte store, and its gates arrive as
+    // 8-byte loads, where the rows' and heads' places allow it.
+    const bool pairs = ((o_stride | o_head | N) & 1) == 0 && ((uintptr_t)out & 3) == 0;
+    const bool gate_pairs = gate && ((gate_stride | gate_partial_stride | gate_off | N) & 1) == 0 && ((uintptr_t)gate & 7) == 0;
 #pragma unroll
     for (int j = 0; j < HM_TN / 8; ++j)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int m = m0 + warp * 16 + g + (i >> 1) * 8, c = n0 + j * 8 + 2 * t + (i & 1);
+        for (int hi = 0; hi < 2; ++hi) {
+            const int m = m0 + warp * 16 + g + hi * 8, c = n0 + j * 8 + 2 * t;
             if (m >= n || c >= N) continue;
-            float v = acc[j][i];
+            float v0 = acc[j][2 * hi], v1 = acc[j][2 * hi + 1];
+            const bool both = c + 1 < N;
             if (gate) {
-                const float gt = mla_slab_sum(gate + (size_t)m * gate_stride, gate_off + h * N + c, gate_partials,
-                                              gate_partial_stride);
-                v = v / (1.0f + expf(-gt));
+                float g0, g1 = 0.0f;
+                const float* gr = gate + (size_t)m * gate_stride;
+                const int gc = gate_off + h * N + c;
+                if (gate_pairs && both) {
+                    float2 sum = *reinterpret_cast<const float2*>(gr + gc);
+                    for (int q = 1; q < gate_partials; ++q) {
+                        const float2 more = *reinterpret_cast<const float2*>(gr + (size_t)q * gate_partial_stride + gc);
+                        sum.x += more.x; sum.y += more.y;
+                    }
+                    g0 = sum.x; g1 = sum.y;
+                } else {
+                    g0 = mla_slab_sum(gr, gc, gate_partials, gate_partial_stride);
+                    if (both) g1 = mla_slab_sum(gr, gc + 1, gate_partials, gate_partial_stride);
+                }
+                v0 = v0 / (1.0f + expf(-g0));
+                v1 = v1 / (1.0f + expf(-g1));
             }
-            out[(size_t)m * o_stride + (size_t)h * o_head + c] = __float2bfloat16(v);
+            __nv_bfloat16* dst = out + (size_t)m * o_stride + (size_t)h * o_head + c;
+            if (pairs && both) {
+                *reinterpret_cast<uint32_t*>(dst) = fb_attn::pack_bf16(v0, v1);
+            } else {
+                dst[0] = __float2bfloat16(v0);
+                if (both) dst[1] = __float2bfloat16(v1);
+            }
         }
     if (r > 0 && blockIdx.y == 0) {
         // the rotated tail: columns K .. K+r of the input row go, turned, to columns N .. N+r of the output row

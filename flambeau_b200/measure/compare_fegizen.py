@@ -24,8 +24,8 @@ Work of one launch over `rows` rows (D = width):
                      that follows rounds once; bfloat16 in Nodepel)
   time_conv          normalised float32 rows in, bfloat16 rows out
   depth_mix          every kept result so far in, the newest and the stream out (averaged over the layers)
-  head_map           2 * rows * heads * in * out flops for the map per head in front of and behind the attention; float32
-                     math on the CUDA cores
+  head_map           2 * rows * heads * in * out flops for the map per head in front of and behind the attention (on
+                     the tensor cores when serving) and the rows it reads and writes
   routed_product     4 * pairs * D * expert inner size flops for both products (6 with a gate); bytes: the weights of the
                      experts that were chosen, once
 """
@@ -119,8 +119,11 @@ def kernel_work(design: str, size: dict, layers: int, rows: int, contexts) -> di
             "norm": dict(bytes=rows * D * (4 + 4 + 4 + 4)),
             "time_conv": dict(bytes=rows * D * (4 + 2)),
             "depth_mix": dict(bytes=rows * D * 4 * ((layers + 3) / 2.0 + 3)),
-            "head_map": dict(fma_flops=2.0 * rows * Ha * size["kv_rank"] * (size["dim"] + size["vdim"]) / 2.0,
-                             bytes=rows * Ha * (row + size["vdim"]) * 2),
+            # (the mean of its two uses: float32 query rows in and latent-sized rows out; those in, value rows out
+            # and the gate's float32 rows in)
+            "head_map": dict(flops=2.0 * rows * Ha * size["kv_rank"] * (size["dim"] + size["vdim"]) / 2.0,
+                             bytes=rows * Ha * ((size["dim"] + size["rot_dim"]) * 4 + 2 * row * 2
+                                                + size["vdim"] * (2 + 4)) / 2.0),
             "routed_product": dict(flops=6.0 * pairs * D * size["expert_ff"],
                                    bytes=experts_read * 3 * D * size["expert_ff"] * 2),
             "expert_combine": dict(bytes=rows * D * 4 * (size["top"] + 2)),
