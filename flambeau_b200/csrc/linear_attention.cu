@@ -71,7 +71,7 @@ template <int R, int LPC> struct GlaTile {
     static constexpr int STAGE_FLOATS = CH * (3 * DKP + COLS);
 };
 
-template <int R, int LPC>
+template <int R, int LPC, bool STATE_BY4>
 __global__ void __launch_bounds__(256)
 gla_recurrent_kernel(const float* __restrict__ qkv, const float* __restrict__ decay, float* __restrict__ state,
                      long state_stride, const int* __restrict__ seq_q_start, const int* __restrict__ seq_q_len,
@@ -121,11 +121,26 @@ gla_recurrent_kernel(const float* __restrict__ qkv, const float* __restrict__ de
     // as one 16-byte vector and neighbouring lanes read neighbouring vectors), else every LPC-th.
     constexpr bool VEC = R % 4 == 0;
     auto channel = [&](int r) { return VEC ? (r / 4) * (4 * LPC) + 4 * li + (r & 3) : li + LPC * r; };
+    // (STATE_BY4: the state moves as 16-byte vectors; the launcher asks for it where a lane's groups of four are whole
+    // and aligned)
     float s[R];
+    if constexpr (STATE_BY4) {
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-        const int d = channel(r);
-        s[r] = (live && d < dk) ? S[d] : 0.0f;
+        for (int r = 0; r < R; r += 4) {
+            const int d = channel(r);
+            float4 x = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (live && d < dk) x = *reinterpret_cast<const float4*>(S + d);
+            s[r] = x.x;
+            if (r + 1 < R) s[r + 1] = x.y;
+            if (r + 2 < R) s[r + 2] = x.z;
+            if (r + 3 < R) s[r + 3] = x.w;
+        }
+    } else {
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const int d = channel(r);
+            s[r] = (live && d < dk) ? S[d] : 0.0f;
+        }
     }
     if (L > 0) fetch(0, sh);
     int buf = 0;
@@ -178,6 +193,16 @@ gla_recurrent_kernel(const float* __restrict__ qkv, const float* __restrict__ de
         }
         __syncthreads();                               // the stage may be overwritten by the fetch after next
     }
+    if constexpr (STATE_BY4) {
+#pragma unroll
+        for (int r = 0; r < R; r += 4) {
+            const int d = channel(r);
+            if (live && d < dk)
+                *reinterpret_cast<float4*>(S + d) = make_float4(s[r], r + 1 < R ? s[r + 1] : 0.0f, r + 2 < R ? s[r + 2] : 0.0f,
+                                                               r + 3 < R ? s[r + 3] : 0.0f);
+        }
+        return;
+    }
 #pragma unroll
     for (int r = 0; r < R; ++r) {
         const int d = channel(r);
@@ -203,25 +228,37 @@ FB_API int fb_gla_prepare(const float* proj, long long proj_stride, int n_partia
 
 template <int R, int LPC>
 static int launch_gla_recurrent(const float* qkv, const float* decay, float* state, long state_stride,
-                                const int* seq_q_start, const int* seq_q_len, const int* seq_slot, int n_seqs, float* o,
-                                int H, int dk, int dv, cudaStream_t stream) {
+                                const int* seq_q_start, const int* seq_q_len, const int* seq_slot, int n_seqs, int rows,
+                                float* o, int H, int dk, int dv, cudaStream_t stream) {
     using Tile = GlaTile<R, LPC>;
     const size_t smem = (size_t)2 * Tile::STAGE_FLOATS * sizeof(float);
-    auto kernel = gla_recurrent_kernel<R, LPC>;
-    if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    fb_launch(kernel, dim3(n_seqs * H, (dv + Tile::COLS - 1) / Tile::COLS), dim3(Tile::THREADS), smem, stream, qkv,
-              decay, state, state_stride, seq_q_start, seq_q_len, seq_slot, o, H, dk, dv);
+    const dim3 grid(n_seqs * H, (dv + Tile::COLS - 1) / Tile::COLS);
+    // The state as 16-byte vectors where a lane's groups of four are whole and aligned, in steps of few tokens a
+    // request, whose time is the state's way in and out; over long portions the variant with plain state loads runs
+    // the token loop faster (measured: 475 against 520 us over 2,048 tokens, 16.2 against 12.3 us for one token).
+    if (R % 4 == 0 && (dk & 3) == 0 && (state_stride & 3) == 0 && ((uintptr_t)state & 15) == 0 &&
+        rows <= 4L * n_seqs) {
+        auto kernel = gla_recurrent_kernel<R, LPC, R % 4 == 0>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        fb_launch(kernel, grid, dim3(Tile::THREADS), smem, stream, qkv, decay, state, state_stride, seq_q_start,
+                  seq_q_len, seq_slot, o, H, dk, dv);
+    } else {
+        auto kernel = gla_recurrent_kernel<R, LPC, false>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        fb_launch(kernel, grid, dim3(Tile::THREADS), smem, stream, qkv, decay, state, state_stride, seq_q_start,
+                  seq_q_len, seq_slot, o, H, dk, dv);
+    }
     return fb_check_launch("gla_recurrent");
 }
 
 FB_API int fb_gla_recurrent(const float* qkv, const float* decay, float* state, long long state_stride,
-                            const int* seq_q_start, const int* seq_q_len, const int* seq_slot, int n_seqs, float* o,
-                            int H, int dk, int dv, cudaStream_t stream) {
-    FB_REQUIRE(n_seqs >= 0 && H > 0 && dk > 0 && dv > 0, "linear attention: bad sizes");
+                            const int* seq_q_start, const int* seq_q_len, const int* seq_slot, int n_seqs, int rows,
+                            float* o, int H, int dk, int dv, cudaStream_t stream) {
+    FB_REQUIRE(n_seqs >= 0 && rows >= 0 && H > 0 && dk > 0 && dv > 0, "linear attention: bad sizes");
     FB_REQUIRE(dk <= 1024, "linear attention: key size %d is larger than 1024", dk);
     if (n_seqs == 0) return 0;
 #define FB_GLA_CASE(R, LPC) return launch_gla_recurrent<R, LPC>(qkv, decay, state, (long)state_stride, seq_q_start, \
-        seq_q_len, seq_slot, n_seqs, o, H, dk, dv, stream)
+        seq_q_len, seq_slot, n_seqs, rows, o, H, dk, dv, stream)
     if (dk <= 16) FB_GLA_CASE(1, 16);
     if (dk <= 32) FB_GLA_CASE(2, 16);
     if (dk <= 64) FB_GLA_CASE(4, 16);

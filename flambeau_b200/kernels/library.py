@@ -68,7 +68,7 @@ _SIGNATURES = {
     "fb_time_conv": (I, [P, P, I, P, L, L, P, P, P, P, I, P, I, I, I, STREAM]),
     # linear_attention.cu
     "fb_gla_prepare": (I, [P, L, I, L, P, P, I, I, F, F, P, P, I, I, I, I, STREAM]),
-    "fb_gla_recurrent": (I, [P, P, P, L, P, P, P, I, P, I, I, I, STREAM]),
+    "fb_gla_recurrent": (I, [P, P, P, L, P, P, P, I, I, P, I, I, I, STREAM]),
     # latent_attention.cu
     "fb_mla_latents": (I, [P, L, I, L, I, P, P, I, I, I, P, I, F, P, P, I, P, P, P, I, P, P, I, I, I, I, P, STREAM]),
     "fb_head_linear": (I, [P, I, L, L, I, L, P, I, P, I, L, L, P, L, I, L, I, P, P, I, I, I, I, I, I, STREAM]),

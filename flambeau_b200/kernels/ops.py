@@ -1093,7 +1093,8 @@ def gla_recurrent(qkv, decay, state, batch, o, H: int, dk: int, dv: int) -> None
         raise KernelError("linear attention: bad output or state")
     check(lib().fb_gla_recurrent(qkv.data_ptr(), decay.data_ptr(), state.data_ptr(), state.stride(0),
                                  batch.seq_q_start_d.data_ptr(), batch.seq_q_len_d.data_ptr(),
-                                 batch.seq_slot_d.data_ptr(), batch.n_seqs, o.data_ptr(), H, dk, dv, _stream()),
+                                 batch.seq_slot_d.data_ptr(), batch.n_seqs, int(qkv.shape[0]), o.data_ptr(), H, dk, dv,
+                                 _stream()),
           "gla_recurrent")
 
 

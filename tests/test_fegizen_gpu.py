@@ -385,7 +385,7 @@ def test_latent_attention_part_and_a_reader_of_its_cache(sizes, dtype):
 
 
 @pytest.mark.parametrize("sizes", [(2, 24, 16, 8.0), (4, 48, 32, 16.0), (1, 40, 8, 2.0), (3, 12, 20, 1.0), (2, 136, 72, 30.0),
-                                   (1, 300, 24, 4.0)], ids=str)
+                                   (1, 300, 24, 4.0), (2, 50, 24, 4.0)], ids=str)
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_gated_linear_attention_part_across_steps(sizes, dtype):
     """The mixer alone with its float32 state slots, two requests in portions, single tokens and pairs; then the
