@@ -59,7 +59,7 @@ def test_centring_norm_with_the_add_in_front(width, dtype):
     assert rel_err(out32, want) < 2e-4
 
 
-@pytest.mark.parametrize("taps", [1, 2, 4, 5])
+@pytest.mark.parametrize("taps", [1, 2, 3, 4, 5])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("layout", [(40, 7, 3), (72, 8, 4)], ids=["ragged", "by16bytes"])
 def test_convolution_over_time_across_steps(taps, dtype, layout):
