@@ -226,3 +226,17 @@ def test_plain_latent_attention_sees_its_window_and_no_more():
     # a reader of these latents with maps of its own: the same (c, kr), other heads
     out, (c2, kr2) = pf.latent_attention(h, w, "m.", m, 1e-6, pos, latent=(c, kr))
     assert torch.allclose(out, ref) and c2 is c and kr2 is kr
+
+
+def test_large_head_groups_are_cut_into_equal_stretches_for_decoded_tokens():
+    """More than 16 query heads on one key/value head: the split-key attention arrangement takes equal stretches of at
+    most 16 heads, and a single token is short for it whatever the group's size."""
+    from flambeau_b200.kernels import ops
+    for heads in range(1, 65):
+        share = ops.attention_kv_share(heads, 1)
+        assert heads % share == 0 and heads // share <= 16
+        assert share == 1 or all(heads % s or heads // s > 16 for s in range(1, share)), "the fewest stretches"
+        assert ops.attention_is_short(1, heads, 1)
+    assert ops.attention_kv_share(32, 1) == 2 and ops.attention_kv_share(64, 2) == 2 and ops.attention_kv_share(17, 1) == 17
+    assert ops.attention_is_short(2, 8, 1) and not ops.attention_is_short(3, 8, 1)
+    assert not ops.attention_is_short(2, 32, 1) and ops.attention_is_short(2, 16, 2)
