@@ -173,7 +173,7 @@ class CacheManager:
                     raise ValueError(f"call {ci} and call {plan.cache_from} disagree on the cache geometry")
                 # pages are given back by the owner's window: a reader that looks further back than the owner
                 # would ask for keys whose pages are gone
-                if plan.kv is not None and src.kv.window > 0 and (plan.kv.window == 0 or plan.kv.window > src.kv.window):
+                if plan.kv is not None and src.kv.release_window > 0 and (plan.kv.window == 0 or plan.kv.window > src.kv.window):
                     raise ValueError(f"call {ci} reads the cache of call {plan.cache_from} with a window of "
                                      f"{plan.kv.window or 'all'} keys, but that cache keeps only {src.kv.window}")
                 continue
@@ -192,15 +192,15 @@ class CacheManager:
             if plan.state is not None:
                 sd = dtype if plan.state.dtype == "engine" else getattr(torch, plan.state.dtype)
                 self.state[ci] = torch.zeros((self.max_requests, *plan.state.shape), dtype=sd, device=device)
-        self.books = Books([g.n_pages for g in self.groups], [g.req.window for g in self.groups], self.page_size,
+        self.books = Books([g.n_pages for g in self.groups], [g.req.release_window for g in self.groups], self.page_size,
                            self.max_requests, self.max_pages_per_request)
         # Columns of a block-table row: the most live pages a request holds in any group.  A group with a window W
         # keeps, while a step of k new tokens runs, the pages from position length - W + 1 to length + k.
         self.table_pages = 1
         for g in self.groups:
             live = self.max_pages_per_request
-            if g.req.window > 0 and self.max_step_tokens:
-                live = min(live, -(-(g.req.window + self.max_step_tokens) // self.page_size) + 2)
+            if g.req.release_window > 0 and self.max_step_tokens:
+                live = min(live, -(-(g.req.release_window + self.max_step_tokens) // self.page_size) + 2)
             self.table_pages = max(self.table_pages, live)
         for g in self.groups:
             g.pool = PoolView(self.books, g.index)

@@ -47,6 +47,8 @@ struct AttnArgs {
     const int* multi_seqs; int n_multi;   // the sequences that bring more than one token, in step order: the grid of
                                           // the arrangements for portions covers only these (nullptr: all n_seqs)
     int nh, nkv, hd, window;
+    int keep_first;                    // under a window: the first keys of a sequence (positions below this) stay
+                                       // visible to every later query, at their true positions; 0: none
     float scale_log2e;
     const float* score_slopes;         // per query head, or nullptr: slope * (key position - query position) is added
                                        // to the scaled score (a linear penalty on distance; <= 0 for the keys a
@@ -84,15 +86,30 @@ __device__ __forceinline__ int table_base_of(const AttnArgs& a, int seq) { retur
 __host__ __device__ __forceinline__ int portion_seqs(const AttnArgs& a) { return a.multi_seqs ? a.n_multi : a.n_seqs; }
 __device__ __forceinline__ int portion_seq(const AttnArgs& a, int j) { return a.multi_seqs ? a.multi_seqs[j] : j; }
 
-// The keys a group of consecutive query tokens [first, last] of a sequence can see, and where tiles start.
-struct KeyRange { int t_lo, t_hi, tile_lo; };
-__device__ __forceinline__ KeyRange key_range(int p_first, int p_last, int window) {
+// The keys a group of consecutive query tokens [first, last] of a sequence can see, and where tiles start.  Under a
+// window that keeps the first `keep` keys visible, the tiles of a group are those that hold kept keys and lie wholly
+// before the window's first tile (`head_tiles` of them, from key 0 on), then the window's tiles from `tile_lo` on.
+struct KeyRange { int t_lo, t_hi, tile_lo, keep, head_tiles; };
+__device__ __forceinline__ KeyRange key_range(int p_first, int p_last, int window, int keep_first = 0) {
     KeyRange r;
     r.t_lo = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
     r.t_hi = p_last;
     r.tile_lo = (r.t_lo / KT) * KT;
+    r.keep = window > 0 ? keep_first : 0;
+    r.head_tiles = min((r.keep + KT - 1) / KT, r.tile_lo / KT);
     return r;
 }
+__device__ __forceinline__ int key_tiles(const KeyRange& r) { return r.head_tiles + (r.t_hi - r.tile_lo) / KT + 1; }
+// The first key of the group's i-th tile.
+__device__ __forceinline__ int key_tile_start(const KeyRange& r, int i) {
+    return i < r.head_tiles ? i * KT : r.tile_lo + (i - r.head_tiles) * KT;
+}
+// Whether some query of the group may see a key of [t_first, t_first + span).
+__device__ __forceinline__ bool keys_wanted(const KeyRange& r, int t_first, int span) {
+    return t_first <= r.t_hi && (t_first + span > r.t_lo || t_first < r.keep);
+}
+// Whether the query at position p, whose window starts at t0, sees key t.
+__device__ __forceinline__ bool key_seen(int t, int p, int t0, int keep) { return t <= p && (t >= t0 || t < keep); }
 
 // Where element (row, dim) of a K/V tile lives in shared memory (dim a multiple of 8).
 //   padded:  rows of HD_MAX + 8 elements (the per-row bulk copies land here);

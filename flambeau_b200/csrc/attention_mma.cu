@@ -83,9 +83,9 @@ attention_mma_kernel(const __grid_constant__ AttnArgs a) {
     const int ntok = min(TQ, q_len - tok0);
     const int q_start = a.seq_q_start[seq], pos0 = a.seq_pos_start[seq];
     const int rows_valid = ntok * G;
-    const KeyRange kr = key_range(pos0 + tok0, pos0 + tok0 + ntok - 1, a.window);
-    const int k_begin = kr.tile_lo, k_end = kr.t_hi + 1, t_hi = kr.t_hi;
-    const int n_tiles = (k_end - k_begin + KT - 1) / KT;
+    const KeyRange kr = key_range(pos0 + tok0, pos0 + tok0 + ntok - 1, a.window, a.keep_first);
+    const int t_hi = kr.t_hi;
+    const int n_tiles = key_tiles(kr);
     const int* table = a.block_table + (size_t)seq * a.table_stride;
     const int base_page = table_base_of(a, seq);
 
@@ -124,7 +124,7 @@ attention_mma_kernel(const __grid_constant__ AttnArgs a) {
             t_first = tile_start + (tid & (KT - 1));
             span = 1;
         }
-        if (!(t_first + span > kr.t_lo && t_first < k_end)) return -2;
+        if (!keys_wanted(kr, t_first, span)) return -2;
         const int page = table_page(a, table, base_page, t_first / a.page_size);
         return (page < 0 || page >= a.n_pages) ? -1 : page;
     };
@@ -170,12 +170,12 @@ attention_mma_kernel(const __grid_constant__ AttnArgs a) {
     };
 
     // prologue: NST - 1 tiles in flight; the page id for the tile after them is already on its way
-    int next_page = lookup(k_begin);
+    int next_page = lookup(key_tile_start(kr, 0));
 #pragma unroll
     for (int st = 0; st < NST - 1; ++st)
         if (st < n_tiles) {
-            load_tile(st, k_begin + st * KT, next_page);
-            next_page = lookup(k_begin + (st + 1) * KT);
+            load_tile(st, key_tile_start(kr, st), next_page);
+            next_page = lookup(key_tile_start(kr, st + 1));
         }
 
     // ---- stage Q (zero-padded) ----
@@ -222,13 +222,13 @@ attention_mma_kernel(const __grid_constant__ AttnArgs a) {
 
     for (int it = 0; it < n_tiles; ++it) {
         const int buf = it % NST;
-        const int tile_start = k_begin + it * KT;
+        const int tile_start = key_tile_start(kr, it);
         if (!mbar_wait(smem_u32(&full[buf]), (uint32_t)(it / NST) & 1u, a.status)) *bail = 1;
         __syncthreads();                              // every thread is past tile it-1: its buffer is free
         if (*bail) break;
         if (it + NST - 1 < n_tiles) {
-            load_tile((it + NST - 1) % NST, tile_start + (NST - 1) * KT, next_page);
-            next_page = lookup(tile_start + NST * KT);    // consumed one iteration from now
+            load_tile((it + NST - 1) % NST, key_tile_start(kr, it + NST - 1), next_page);
+            next_page = lookup(key_tile_start(kr, it + NST));    // consumed one iteration from now
         }
         if constexpr (TMA) {
             // Whole pages arrive, the slots behind the last position included, and what a page holds there was
@@ -288,7 +288,7 @@ attention_mma_kernel(const __grid_constant__ AttnArgs a) {
                 for (int e = 0; e < 4; ++e) {
                     const int h = e >> 1;
                     const int t = tile_start + nb * 8 + 2 * (lane & 3) + (e & 1);
-                    const bool ok = t >= t0_row[rb][h] && t <= p_row[rb][h] && t < k_end;
+                    const bool ok = key_seen(t, p_row[rb][h], t0_row[rb][h], kr.keep);
                     const float v = ok ? fmaf(slope_row[rb][h], (float)(t - p_row[rb][h]), s[rb][nb][e] * a.scale_log2e) : -INFINITY;
                     s[rb][nb][e] = v;
                     tile_max[h] = fmaxf(tile_max[h], v);
@@ -460,7 +460,7 @@ FB_API int fb_paged_attention_mma(const void* q, long long q_stride, void* out, 
                                   const int* block_table, int table_stride, const int* table_base,
                                   const int* seq_q_start, const int* seq_q_len, const int* seq_pos_start,
                                   const int* multi_seqs, int n_multi, int n_seqs, int max_q_len, int max_kv_len, int any_short, int any_long, int nh, int nkv, int hd,
-                                  int window, float scale, const float* score_slopes, const float* sinks,
+                                  int window, int keep_first, float scale, const float* score_slopes, const float* sinks,
                                   int weights_hi_lo, float* scratch,
                                   long long scratch_floats,
                                   const void* prefetch_base, long long prefetch_rows, long long prefetch_row_stride,
@@ -473,7 +473,7 @@ FB_API int fb_paged_attention_mma(const void* q, long long q_stride, void* out, 
     FB_REQUIRE(G <= 64, "attention_mma: %d query heads per key/value head exceed 64", G);
     FB_REQUIRE(q_stride % 8 == 0 && ((uintptr_t)q & 15) == 0, "attention_mma: q rows must be 16-byte aligned");
     FB_REQUIRE(out_stride % 2 == 0 && ((uintptr_t)out & 3) == 0, "attention_mma: out rows must be 4-byte aligned");
-    FB_REQUIRE(page_size > 0 && n_pages > 0 && window >= 0, "attention_mma: bad cache geometry");
+    FB_REQUIRE(page_size > 0 && n_pages > 0 && window >= 0 && keep_first >= 0, "attention_mma: bad cache geometry");
     if (n_seqs == 0) return 0;
     const int HD_MAX = hd <= 32 ? 32 : hd <= 64 ? 64 : hd <= 128 ? 128 : 256;
     AttnArgs a;
@@ -485,6 +485,7 @@ FB_API int fb_paged_attention_mma(const void* q, long long q_stride, void* out, 
     a.seq_q_start = seq_q_start; a.seq_q_len = seq_q_len; a.seq_pos_start = seq_pos_start;
     a.multi_seqs = multi_seqs; a.n_multi = n_multi;
     a.nh = nh; a.nkv = nkv; a.hd = hd; a.window = window;
+    a.keep_first = window > 0 ? keep_first : 0;
     a.scale_log2e = scale * 1.4426950408889634f;
     a.score_slopes = score_slopes;
     a.sinks = sinks;

@@ -25,7 +25,7 @@ paged_attention_simt_kernel(const T* __restrict__ q, long q_stride, T* __restric
                             int n_pages, const int* __restrict__ block_table, int table_stride,
                             const int* __restrict__ table_base,
                             const int* __restrict__ positions, const int* __restrict__ row_seq, int n, int nh,
-                            int nkv, int hd, int vd, int window, float scale,
+                            int nkv, int hd, int vd, int window, int keep_first, float scale,
                             const float* __restrict__ score_slopes, const float* __restrict__ sinks, int* status) {
     fb_pdl_launch_dependents();
     fb_pdl_wait();
@@ -55,9 +55,13 @@ paged_attention_simt_kernel(const T* __restrict__ q, long q_stride, T* __restric
 #pragma unroll
     for (int r = 0; r < NDR; ++r) acc[r] = 0.0f;
 
-    for (int base = t0; base <= p; base += 32) {
+    // Two stretches of keys: the kept first ones that lie before the window (none without a window), then the window.
+    const int keep_end = min(window > 0 ? keep_first : 0, t0);
+    for (int stretch = keep_end > 0 ? 0 : 1; stretch < 2; ++stretch) {
+    const int first = stretch == 0 ? 0 : t0, stop = stretch == 0 ? keep_end - 1 : p;    // this stretch's keys
+    for (int base = first; base <= stop; base += 32) {
         const int t = base + lane;
-        const bool valid = t <= p;
+        const bool valid = t <= stop;
         float s = -INFINITY;
         int my_page = -1;
         if (valid) {
@@ -81,7 +85,7 @@ paged_attention_simt_kernel(const T* __restrict__ q, long q_stride, T* __restric
         l = l * corr + fb_warp_sum(pr);
 #pragma unroll
         for (int r = 0; r < NDR; ++r) acc[r] *= corr;
-        const int count = min(32, p - base + 1);
+        const int count = min(32, stop - base + 1);
         for (int j = 0; j < count; ++j) {
             const float pj = __shfl_sync(0xffffffffu, pr, j);
             const int page_j = __shfl_sync(0xffffffffu, my_page, j);
@@ -95,6 +99,7 @@ paged_attention_simt_kernel(const T* __restrict__ q, long q_stride, T* __restric
             }
         }
         m = m_new;
+    }
     }
     if (sinks) {                                        // the slot without key and value
         const float sk = sinks[head];
@@ -118,13 +123,13 @@ static int launch_attention_simt(const void* q, long q_stride, void* out, long o
                                  const void* v_pool, int page_size, int n_pages, const int* block_table,
                                  int table_stride, const int* table_base, const int* positions, const int* row_seq,
                                  int n, int nh,
-                                 int nkv, int hd, int vd, int window, float scale, const float* score_slopes,
+                                 int nkv, int hd, int vd, int window, int keep_first, float scale, const float* score_slopes,
                                  const float* sinks, int* status, cudaStream_t stream) {
     const long items = (long)n * nh;
     const unsigned blocks = (unsigned)((items + 3) / 4);
     fb_launch((paged_attention_simt_kernel<T, NDR>), blocks, 128, 4 * hd * sizeof(float), stream, 
         (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_pool, (const T*)v_pool, page_size, n_pages,
-        block_table, table_stride, table_base, positions, row_seq, n, nh, nkv, hd, vd, window, scale, score_slopes, sinks,
+        block_table, table_stride, table_base, positions, row_seq, n, nh, nkv, hd, vd, window, keep_first, scale, score_slopes, sinks,
         status);
     return fb_check_launch("paged_attention_simt");
 }
@@ -133,18 +138,18 @@ FB_API int fb_paged_attention_simt(const void* q, long long q_stride, void* out,
                                    const void* k_pool, const void* v_pool, int page_size, int n_pages,
                                    const int* block_table, int table_stride, const int* table_base,
                                    const int* positions, const int* row_seq, int n, int nh, int nkv, int hd,
-                                   int vd, int window, float scale, const float* score_slopes, const float* sinks,
+                                   int vd, int window, int keep_first, float scale, const float* score_slopes, const float* sinks,
                                    int* status, cudaStream_t stream) {
     if (vd <= 0) vd = hd;
     FB_REQUIRE(n >= 0 && nh > 0 && nkv > 0 && hd > 0, "attention: bad sizes n=%d heads=%d kv=%d hd=%d", n, nh, nkv, hd);
     FB_REQUIRE(nh % nkv == 0, "attention: %d query heads are not a multiple of %d key/value heads", nh, nkv);
     FB_REQUIRE(hd <= 512 && vd <= 512, "attention: head size %d / value size %d is larger than 512", hd, vd);
-    FB_REQUIRE(page_size > 0 && n_pages > 0 && window >= 0, "attention: bad cache geometry");
+    FB_REQUIRE(page_size > 0 && n_pages > 0 && window >= 0 && keep_first >= 0, "attention: bad cache geometry");
     if (n == 0) return 0;
 #define FB_ATTN_CASE(NDR)                                                                                      \
     FB_DISPATCH_DTYPE(dtype, T, return (launch_attention_simt<T, NDR>(q, (long)q_stride, out, (long)out_stride,     \
         k_pool, v_pool, page_size, n_pages, block_table, table_stride, table_base, positions, row_seq, n, nh, \
-        nkv, hd, vd, window, scale, score_slopes, sinks, status, stream)))
+        nkv, hd, vd, window, keep_first, scale, score_slopes, sinks, status, stream)))
     if (vd <= 32) { FB_ATTN_CASE(1); }
     else if (vd <= 64) { FB_ATTN_CASE(2); }
     else if (vd <= 128) { FB_ATTN_CASE(4); }

@@ -36,8 +36,7 @@ using namespace fb_attn;
 
 __device__ __forceinline__ int short_tiles_of(const AttnArgs& a, int q_len, int pos0, int G) {
     if (q_len * G > a.short_rows) return 0;                 // belongs to the arrangement for portions
-    const KeyRange kr = key_range(pos0, pos0 + q_len - 1, a.window);
-    return (kr.t_hi - kr.tile_lo) / KT + 1;
+    return key_tiles(key_range(pos0, pos0 + q_len - 1, a.window, a.keep_first));
 }
 
 // Per-sequence facts in shared memory: five arrays of n_seqs (+1) ints.
@@ -194,7 +193,8 @@ attention_split_kernel(const __grid_constant__ AttnArgs a) {
     int cur_seq = 0;
 
     struct Seg {
-        int seq, kvh, q_len, q_start, pos0, t_lo, t_hi, k_begin, k_end, n_tiles;
+        int seq, kvh, q_len, q_start, pos0, t_hi, tile_a, n_tiles;
+        KeyRange kr;                       // the pair's keys; this segment is its tiles [tile_a, tile_a + n_tiles)
         int c_first, n_chunks;             // the first CTA with a segment of this pair, and how many have one
         const int* table;
         int base_page;                     // the logical page that column 0 of the table row stands for
@@ -208,10 +208,9 @@ attention_split_kernel(const __grid_constant__ AttnArgs a) {
         const int tile_b = min(n, tile_a + (seg_hi - g));
         g += tile_b - tile_a;
         sg.seq = seq; sg.kvh = kvh; sg.q_len = ss.q_len[seq]; sg.q_start = ss.q_start[seq]; sg.pos0 = ss.pos0[seq];
-        const KeyRange kr = key_range(sg.pos0, sg.pos0 + sg.q_len - 1, a.window);
-        sg.t_lo = kr.t_lo; sg.t_hi = kr.t_hi;
-        sg.k_begin = kr.tile_lo + tile_a * KT;
-        sg.k_end = min(kr.t_hi + 1, kr.tile_lo + tile_b * KT);
+        sg.kr = key_range(sg.pos0, sg.pos0 + sg.q_len - 1, a.window, a.keep_first);
+        sg.t_hi = sg.kr.t_hi;
+        sg.tile_a = tile_a;
         sg.n_tiles = tile_b - tile_a;
         sg.table = a.block_table + (size_t)seq * a.table_stride;
         sg.base_page = table_base_of(a, seq);
@@ -273,7 +272,7 @@ attention_split_kernel(const __grid_constant__ AttnArgs a) {
                 int t_first, span;
                 if (TMA) { t_first = tile_start + ((op >> 1) / col_blocks) * a.page_size; span = a.page_size; }
                 else { t_first = tile_start + (op & (KT - 1)); span = 1; }
-                if (!(t_first + span > sg.t_lo && t_first < sg.k_end)) continue;
+                if (!keys_wanted(sg.kr, t_first, span)) continue;
                 const int page = table_page(a, sg.table, sg.base_page, t_first / a.page_size);
                 pages[u] = (page < 0 || page >= a.n_pages) ? -1 : page;
             }
@@ -321,15 +320,15 @@ attention_split_kernel(const __grid_constant__ AttnArgs a) {
         Seg sg = next_seg();
         int it = 0;
         bool waited = false;
-        lookup(sg, sg.k_begin);
+        lookup(sg, key_tile_start(sg.kr, sg.tile_a));
         for (uint32_t count = 0;; ++count) {
             const int buf = (int)(count % NST);
             if (count >= NST && !wait(&empty[buf], ((count / NST) - 1) & 1u)) return;
-            if (!waited && sg.k_begin + (it + 1) * KT > sg.pos0) {
+            if (!waited && key_tile_start(sg.kr, sg.tile_a + it) + KT > sg.pos0) {
                 fb_pdl_wait();
                 waited = true;
             }
-            issue(sg, buf, sg.k_begin + it * KT);
+            issue(sg, buf, key_tile_start(sg.kr, sg.tile_a + it));
             if (++it == sg.n_tiles) {
                 if (g >= seg_hi) {
                     // the stream of cache ends here: the memory system is free for the product that follows
@@ -339,7 +338,7 @@ attention_split_kernel(const __grid_constant__ AttnArgs a) {
                 sg = next_seg();
                 it = 0;
             }
-            lookup(sg, sg.k_begin + it * KT);         // in flight while this warp waits for the slot
+            lookup(sg, key_tile_start(sg.kr, sg.tile_a + it));         // in flight while this warp waits for the slot
         }
     }
 
@@ -349,7 +348,7 @@ attention_split_kernel(const __grid_constant__ AttnArgs a) {
     uint32_t count = 0;                               // tiles consumed: slot and barrier phase follow from it
     Seg cur = next_seg();
     for (;;) {
-        const int kvh = cur.kvh, q_start = cur.q_start, pos0 = cur.pos0, k_begin = cur.k_begin, k_end = cur.k_end;
+        const int kvh = cur.kvh, q_start = cur.q_start, pos0 = cur.pos0;
         const int rows_valid = cur.q_len * G;
         // ---- stage Q (zero-padded) ----
         for (int idx = tid; idx < 16 * (HD_MAX / 8); idx += 32 * SPLIT_SCORERS) {
@@ -393,7 +392,7 @@ attention_split_kernel(const __grid_constant__ AttnArgs a) {
         for (int it = 0; it < cur.n_tiles; ++it) {
             const uint32_t seen = count + (uint32_t)it;
             const int buf = (int)(seen % NST);
-            const int tile_start = k_begin + it * KT;
+            const int tile_start = key_tile_start(cur.kr, cur.tile_a + it);
             if (wait(&full[buf], (seen / NST) & 1u)) {
                 const __nv_bfloat16* kt = k_tile(buf);
                 __nv_bfloat16* vt = v_tile(buf);
@@ -447,7 +446,7 @@ attention_split_kernel(const __grid_constant__ AttnArgs a) {
                     for (int e = 0; e < 4; ++e) {
                         const int h = e >> 1;
                         const int t = tile_start + key0 + nb * 8 + 2 * (lane & 3) + (e & 1);
-                        const bool ok = t >= t0_row[h] && t <= p_row[h] && t < k_end;
+                        const bool ok = key_seen(t, p_row[h], t0_row[h], cur.kr.keep);
                         const float v = ok ? fmaf(slope_row[h], (float)(t - p_row[h]), s[nb][e] * a.scale_log2e) : -INFINITY;
                         s[nb][e] = v;
                         tile_max[h] = fmaxf(tile_max[h], v);

@@ -453,7 +453,8 @@ int launch_tc(const AttnArgs& a, int n_seqs, int max_q_len, cudaStream_t stream)
 bool fb_attention_tc_takes(const AttnArgs& a, bool tma) {
     const int G = a.nh / a.nkv;
     // (its weights are bfloat16 in tensor memory: steps that want them in two parts run on the mma.sync kernel)
-    return tma && !a.score_slopes && !a.weights_hi_lo && (a.hd == 64 || a.hd == 128) && G <= BM && BN % a.page_size == 0 &&
+    // (nor does it walk kept first keys behind a window)
+    return tma && !a.score_slopes && !a.weights_hi_lo && a.keep_first == 0 && (a.hd == 64 || a.hd == 128) && G <= BM && BN % a.page_size == 0 &&
            a.out_stride % 8 == 0 &&
            (reinterpret_cast<uintptr_t>(a.out) & 15) == 0;
 }

@@ -885,6 +885,53 @@ FB_API int fb_activation(const void* z, long long stride, int in_dtype, int n_pa
 }
 
 // ---------------------------------------------------------------------------
+// a[r, c] *= sigmoid(g[r, c]) in place: an output gate on a mixer's heads, the gate being columns of a product that
+// arrives as float32 split-K shares (added first).  Four columns a thread where rows and widths allow it.
+// ---------------------------------------------------------------------------
+template <typename T, int VEC>
+__global__ void sigmoid_gate_kernel(T* __restrict__ a, long a_stride, const float* __restrict__ g, long g_stride,
+                                    int n_partials, long partial_stride, int n, int I) {
+    fb_pdl_launch_dependents();
+    fb_pdl_wait();
+    const int per = I / VEC;
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)n * per) return;
+    const int r = (int)(idx / per), c = (int)(idx - (size_t)r * per) * VEC;
+    const float* gr = g + (size_t)r * g_stride + c;
+    T* ar = a + (size_t)r * a_stride + c;
+    if constexpr (VEC == 4) {
+        const float4 z = slab_sum4(gr, n_partials, partial_stride);
+        float4 v = Vec4<T>::load(ar);
+        v.x = v.x / (1.0f + expf(-z.x)); v.y = v.y / (1.0f + expf(-z.y));
+        v.z = v.z / (1.0f + expf(-z.z)); v.w = v.w / (1.0f + expf(-z.w));
+        Vec4<T>::store(ar, v);
+    } else {
+        const float z = slab_sum(gr, 0, n_partials, partial_stride);
+        ar[0] = fb_from_float<T>(fb_to_float(ar[0]) / (1.0f + expf(-z)));
+    }
+}
+
+FB_API int fb_sigmoid_gate(void* a, long long a_stride, int dtype, const float* g, long long g_stride, int n_partials,
+                           long long partial_stride, int n, int I, cudaStream_t stream) {
+    FB_REQUIRE(n >= 0 && I > 0 && a_stride >= I && g_stride >= I, "sigmoid_gate: bad sizes n=%d I=%d", n, I);
+    if (n == 0) return 0;
+    if (n_partials < 1) n_partials = 1;
+    const bool vec = I % 4 == 0 && a_stride % 4 == 0 && g_stride % 4 == 0 && partial_stride % 4 == 0 &&
+                     (uintptr_t)a % 16 == 0 && (uintptr_t)g % 16 == 0;
+    const size_t total = (size_t)n * (vec ? I / 4 : I);
+    if (vec) {
+        FB_DISPATCH_DTYPE(dtype, T,
+            (fb_launch((sigmoid_gate_kernel<T, 4>), (unsigned)((total + 255) / 256), 256, 0, stream, (T*)a, (long)a_stride,
+                       g, (long)g_stride, n_partials, (long)partial_stride, n, I)));
+    } else {
+        FB_DISPATCH_DTYPE(dtype, T,
+            (fb_launch((sigmoid_gate_kernel<T, 1>), (unsigned)((total + 255) / 256), 256, 0, stream, (T*)a, (long)a_stride,
+                       g, (long)g_stride, n_partials, (long)partial_stride, n, I)));
+    }
+    return fb_check_launch("sigmoid_gate");
+}
+
+// ---------------------------------------------------------------------------
 // x[r, :] += v[:] for the first n rows of the float32 stream (a learned vector that joins every token alike).
 // ---------------------------------------------------------------------------
 template <typename TW>

@@ -574,6 +574,42 @@ FB_API int fb_gemm_tc_gated(const void* X, long long lda, const void* W, long lo
     return fb_fail(-1, "gemm_tc_gated: unknown output dtype code %d", o_dtype);
 }
 
+// out[M, N] = act(X[M,K] * W[N,K]^T) with `act` a plain activation (an FbPlainAct code) applied in the epilogue: the
+// first product of a feed-forward without a gate (the whole sum in one CTA, so K is not split).
+FB_API int fb_gemm_tc_act(const void* X, long long lda, const void* W, long long ldw, void* out, int o_dtype,
+                          long long ldo, int M, int N, int K, int act, int* status, cudaStream_t stream) {
+    FB_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm_tc_act: bad sizes M=%d N=%d K=%d", M, N, K);
+    FB_REQUIRE(fb_plain_act_known(act) && act != FB_PLAIN_NONE, "gemm_tc_act: unknown activation code %d", act);
+    FB_REQUIRE(lda >= K && ldw >= K && ldo >= N, "gemm_tc_act: a row stride is shorter than its row");
+    FB_REQUIRE(lda % 8 == 0 && ldw % 8 == 0, "gemm_tc_act: row strides must be multiples of 8 elements");
+    FB_REQUIRE(((uintptr_t)X & 15) == 0 && ((uintptr_t)W & 15) == 0, "gemm_tc_act: operands must be 16-byte aligned");
+    if (M == 0) return 0;
+    const int BN = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+    CUtensorMap mw, mx;
+    int rc = fb_tensor_map_bf16(&mw, W, N, K, (long)ldw, BK, BM);
+    if (rc) return rc;
+    rc = fb_tensor_map_bf16(&mx, X, M, K, (long)lda, BK, BN);
+    if (rc) return rc;
+#define FB_TCA_CASE(BN_)                                                                                        \
+    case BN_:                                                                                                   \
+        if (o_dtype == FB_F32)                                                                                  \
+            return launch_tc<BN_, float, true>(mw, mx, out, (long)ldo, 0, 1, nullptr, nullptr, 0, nullptr, 0, M, N, K, \
+                                               1, status, stream, 0, nullptr, 0, act);                          \
+        else if (o_dtype == FB_BF16)                                                                            \
+            return launch_tc<BN_, __nv_bfloat16, true>(mw, mx, out, (long)ldo, 0, 1, nullptr, nullptr, 0, nullptr, 0, \
+                                                       M, N, K, 1, status, stream, 0, nullptr, 0, act);         \
+        break;
+    switch (BN) {
+        FB_TCA_CASE(16)
+        FB_TCA_CASE(32)
+        FB_TCA_CASE(64)
+        FB_TCA_CASE(128)
+        FB_TCA_CASE(256)
+    }
+#undef FB_TCA_CASE
+    return fb_fail(-1, "gemm_tc_act: unknown output dtype code %d", o_dtype);
+}
+
 // ---------------------------------------------------------------------------
 // The product for callers that must not allocate (declared and described in no_alloc.h; no counterpart in the
 // reference).  Same kernel and launcher as fb_gemm_tc in its meet-in-scratch form; the scratch is this array.

@@ -17,21 +17,25 @@
 //                 `a` may be float32 shares (added first).  Two optional extras: K..K+r of the input row rotated into
 //                 N..N+r of the output row (the query side), and the result multiplied by sigmoid of a gate taken
 //                 from another product's shares (the output side).
-// Rotation pairs neighbours: (x[2i], x[2i+1]) -> (x[2i] cos - x[2i+1] sin, x[2i+1] cos + x[2i] sin), i < half, with
-// per-token tables; dimensions from 2 half on pass unchanged.
+// Rotation turns pair i < half of the rotated part, (u, v) -> (u cos - v sin, v cos + u sin), with per-token tables;
+// `pairing` says which dimensions form pair i: 0 neighbours (2i, 2i + 1), 1 halves (i, i + half).  Dimensions from
+// 2 half on pass unchanged.
 #include "common.cuh"
 #include "attention_common.cuh"
 
 __device__ __forceinline__ float mla_slab_sum(const float* row, int c, int n_partials, long partial_stride) {
     return fb_slab_sum(row, c, n_partials, partial_stride);
 }
+// The two dimensions of pair i of a rotated vector with `half` pairs.
+__device__ __forceinline__ int rot_first(int pairing, int i) { return pairing ? i : 2 * i; }
+__device__ __forceinline__ int rot_second(int pairing, int i, int half) { return pairing ? i + half : 2 * i + 1; }
 
 template <typename TW, typename TO>
 __global__ void __launch_bounds__(256)
 mla_latents_kernel(const float* __restrict__ proj, long proj_stride, int n_partials, long partial_stride, int Rq,
                    const TW* __restrict__ wq, TO* __restrict__ cq, int kv_off, int Rc, int r,
                    const TW* __restrict__ wkv, float eps, const float* __restrict__ cos_t,
-                   const float* __restrict__ sin_t, int half, const int* __restrict__ positions,
+                   const float* __restrict__ sin_t, int half, int pairing, const int* __restrict__ positions,
                    const int* __restrict__ row_seq, const int* __restrict__ block_table, int table_stride,
                    const int* __restrict__ table_base, TO* __restrict__ pool, int page_size, int n_pages, int* status) {
     fb_pdl_launch_dependents();
@@ -71,11 +75,12 @@ mla_latents_kernel(const float* __restrict__ proj, long proj_stride, int n_parti
     const float* kr = pr + kv_off + Rc;
     for (int i = tid; i < r - half; i += blockDim.x) {
         if (i < half) {
-            const float u = mla_slab_sum(kr, 2 * i, n_partials, partial_stride);
-            const float v = mla_slab_sum(kr, 2 * i + 1, n_partials, partial_stride);
+            const int iu = rot_first(pairing, i), iv = rot_second(pairing, i, half);
+            const float u = mla_slab_sum(kr, iu, n_partials, partial_stride);
+            const float v = mla_slab_sum(kr, iv, n_partials, partial_stride);
             const float c = cos_t[(size_t)t * half + i], s = sin_t[(size_t)t * half + i];
-            dst[Rc + 2 * i] = fb_from_float<TO>(u * c - v * s);
-            dst[Rc + 2 * i + 1] = fb_from_float<TO>(v * c + u * s);
+            dst[Rc + iu] = fb_from_float<TO>(u * c - v * s);
+            dst[Rc + iv] = fb_from_float<TO>(v * c + u * s);
         } else {
             dst[Rc + half + i] = fb_from_float<TO>(mla_slab_sum(kr, half + i, n_partials, partial_stride));
         }
@@ -90,7 +95,7 @@ head_linear_kernel(const TA* __restrict__ a, long a_stride, long a_head, int n_p
                    const TW* __restrict__ w, TO* __restrict__ out, long o_stride, long o_head,
                    const float* __restrict__ gate, long gate_stride, int gate_partials, long gate_partial_stride,
                    int gate_off, const float* __restrict__ cos_t, const float* __restrict__ sin_t, int half, int r,
-                   int n, int N, int K) {
+                   int pairing, int n, int N, int K) {
     fb_pdl_launch_dependents();
     fb_pdl_wait();
     __shared__ float As[HL_KC][HL_TM + 1];
@@ -165,10 +170,11 @@ head_linear_kernel(const TA* __restrict__ a, long a_stride, long a_head, int n_p
                 return v;
             };
             if (i < half) {
-                const float u = in(2 * i), v = in(2 * i + 1);
+                const int iu = rot_first(pairing, i), iv = rot_second(pairing, i, half);
+                const float u = in(iu), v = in(iv);
                 const float c = cos_t[(size_t)m * half + i], s = sin_t[(size_t)m * half + i];
-                dst[2 * i] = fb_from_float<TO>(u * c - v * s);
-                dst[2 * i + 1] = fb_from_float<TO>(v * c + u * s);
+                dst[iu] = fb_from_float<TO>(u * c - v * s);
+                dst[iv] = fb_from_float<TO>(v * c + u * s);
             } else {
                 dst[half + i] = fb_from_float<TO>(in(half + i));
             }
@@ -188,7 +194,7 @@ head_linear_mma_kernel(const TA* __restrict__ a, long a_stride, long a_head, int
                        const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out, long o_stride, long o_head,
                        const float* __restrict__ gate, long gate_stride, int gate_partials, long gate_partial_stride,
                        int gate_off, const float* __restrict__ cos_t, const float* __restrict__ sin_t, int half, int r,
-                       int n, int N, int K, int a_vec, int w_vec) {
+                       int pairing, int n, int N, int K, int a_vec, int w_vec) {
     fb_pdl_launch_dependents();
     fb_pdl_wait();
     __shared__ __align__(16) __nv_bfloat16 As[HM_TM][HM_LD];
@@ -359,10 +365,11 @@ head_linear_mma_kernel(const TA* __restrict__ a, long a_stride, long a_head, int
                 return v;
             };
             if (i < half) {
-                const float u = in(2 * i), v = in(2 * i + 1);
+                const int iu = rot_first(pairing, i), iv = rot_second(pairing, i, half);
+                const float u = in(iu), v = in(iv);
                 const float c = cos_t[(size_t)m * half + i], s = sin_t[(size_t)m * half + i];
-                dst[2 * i] = __float2bfloat16(u * c - v * s);
-                dst[2 * i + 1] = __float2bfloat16(v * c + u * s);
+                dst[iu] = __float2bfloat16(u * c - v * s);
+                dst[iv] = __float2bfloat16(v * c + u * s);
             } else {
                 dst[half + i] = __float2bfloat16(in(half + i));
             }
@@ -374,12 +381,13 @@ head_linear_mma_kernel(const TA* __restrict__ a, long a_stride, long a_head, int
 // cache row is written as well ([pages][1][page size][Rc + r], engine dtype); without it only the query's latent.
 FB_API int fb_mla_latents(const float* proj, long long proj_stride, int n_partials, long long partial_stride, int Rq,
                           const void* wq, void* cq, int kv_off, int Rc, int r, const void* wkv, int w_dtype, float eps,
-                          const float* cos_t, const float* sin_t, int half, const int* positions, const int* row_seq,
-                          const int* block_table, int table_stride, const int* table_base, void* pool, int out_dtype,
+                          const float* cos_t, const float* sin_t, int half, int pairing, const int* positions,
+                          const int* row_seq, const int* block_table, int table_stride, const int* table_base, void* pool, int out_dtype,
                           int page_size, int n_pages, int n, int* status, cudaStream_t stream) {
     FB_REQUIRE(n >= 0 && Rq > 0 && Rc > 0 && r >= 0 && half >= 0 && 2 * half <= r, "latent attention: bad sizes");
     FB_REQUIRE(eps > 0.0f, "latent attention: eps must be positive");
     FB_REQUIRE(half == 0 || (cos_t && sin_t), "latent attention: a rotation needs its tables");
+    FB_REQUIRE(pairing == 0 || pairing == 1, "latent attention: pairs are neighbours (0) or halves (1)");
     FB_REQUIRE(!pool || (block_table && positions && row_seq && wkv), "latent attention: a cache write needs the step's tables");
     if (n == 0) return 0;
     if (n_partials < 1) n_partials = 1;
@@ -388,7 +396,7 @@ FB_API int fb_mla_latents(const float* proj, long long proj_stride, int n_partia
     FB_DISPATCH_DTYPE(w_dtype, TW, FB_DISPATCH_DTYPE(out_dtype, TO,
         (fb_launch((mla_latents_kernel<TW, TO>), dim3(n, pool ? 2 : 1), dim3(256), smem, stream, proj, (long)proj_stride,
                    n_partials, (long)partial_stride, Rq, (const TW*)wq, (TO*)cq, kv_off, Rc, r, (const TW*)wkv, eps,
-                   cos_t, sin_t, half, positions, row_seq, block_table, table_stride, table_base, (TO*)pool, page_size,
+                   cos_t, sin_t, half, pairing, positions, row_seq, block_table, table_stride, table_base, (TO*)pool, page_size,
                    n_pages, status))));
     return fb_check_launch("mla_latents");
 }
@@ -398,10 +406,11 @@ FB_API int fb_head_linear(const void* a, int a_dtype, long long a_stride, long l
                           long long partial_stride, const void* w, int w_dtype, void* out, int out_dtype,
                           long long o_stride, long long o_head, const float* gate, long long gate_stride,
                           int gate_partials, long long gate_partial_stride, int gate_off, const float* cos_t,
-                          const float* sin_t, int half, int r, int n, int H, int N, int K, cudaStream_t stream) {
+                          const float* sin_t, int half, int r, int pairing, int n, int H, int N, int K, cudaStream_t stream) {
     FB_REQUIRE(n >= 0 && H > 0 && N > 0 && K > 0 && r >= 0 && half >= 0 && 2 * half <= r, "head_linear: bad sizes");
     FB_REQUIRE(n_partials <= 1 || a_dtype == FB_F32, "head_linear: only float32 inputs come as shares");
     FB_REQUIRE(half == 0 || (cos_t && sin_t), "head_linear: a rotation needs its tables");
+    FB_REQUIRE(pairing == 0 || pairing == 1, "head_linear: pairs are neighbours (0) or halves (1)");
     FB_REQUIRE(H <= 65535 && (N + HL_TN - 1) / HL_TN <= 65535, "head_linear: too many heads or outputs");
     if (n == 0) return 0;
     if (n_partials < 1) n_partials = 1;
@@ -417,7 +426,7 @@ FB_API int fb_head_linear(const void* a, int a_dtype, long long a_stride, long l
             (fb_launch((head_linear_mma_kernel<TA>), tiles, dim3(128), 0, stream, (const TA*)a, (long)a_stride,
                        (long)a_head, n_partials, (long)partial_stride, (const __nv_bfloat16*)w, (__nv_bfloat16*)out,
                        (long)o_stride, (long)o_head, gate, (long)gate_stride, gate_partials, (long)gate_partial_stride,
-                       gate_off, cos_t, sin_t, half, r, n, N, K, a_vec, w_vec)));
+                       gate_off, cos_t, sin_t, half, r, pairing, n, N, K, a_vec, w_vec)));
         return fb_check_launch("head_linear");
     }
     const dim3 grid((n + HL_TM - 1) / HL_TM, (N + HL_TN - 1) / HL_TN, H);
@@ -425,7 +434,7 @@ FB_API int fb_head_linear(const void* a, int a_dtype, long long a_stride, long l
         (fb_launch((head_linear_kernel<TA, TW, TO>), grid, dim3(256), 0, stream, (const TA*)a, (long)a_stride,
                    (long)a_head, n_partials, (long)partial_stride, (const TW*)w, (TO*)out, (long)o_stride, (long)o_head,
                    gate, (long)gate_stride, gate_partials, (long)gate_partial_stride, gate_off, cos_t, sin_t, half, r,
-                   n, N, K)))));
+                   pairing, n, N, K)))));
     return fb_check_launch("head_linear");
 }
 

@@ -173,7 +173,7 @@ class Scheduler:
     def _pages_for(self, tokens: int, group: int) -> int:
         """Pages that `tokens` tokens of one request hold in a group at most (a window keeps the last W tokens,
         plus the portion that is being written and the page the window starts in)."""
-        window = self.cache.groups[group].req.window
+        window = self.cache.groups[group].req.release_window
         page = self.cache.page_size
         if window:
             tokens = min(tokens, window + self.prefill_chunk + page)

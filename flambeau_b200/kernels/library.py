@@ -36,6 +36,9 @@ _SIGNATURES = {
     "fb_activation": (I, [P, L, I, I, L, P, I, I, I, I, STREAM]),
     "fb_add_row": (I, [P, P, I, I, I, STREAM]),
     "fb_add_slabs": (I, [P, P, I, L, I, I, STREAM]),
+    "fb_sigmoid_gate": (I, [P, L, I, P, L, I, L, I, I, STREAM]),
+    # hyper_connections.cu
+    "fb_hc_step": (I, [P, L, I, P, I, L, P, P, P, P, I, F, F, P, I, P, I, I, I, STREAM]),
     "fb_branch_norm_mix": (I, [I, P, P, P, P, I, P, F, F, P, I, I, STREAM]),
     # gemm_simt.cu
     "fb_gemm_simt": (I, [P, I, L, P, I, L, P, I, L, I, I, I, STREAM]),
@@ -45,9 +48,10 @@ _SIGNATURES = {
     "fb_gemm_tc": (I, [P, L, P, L, P, I, L, L, I, P, I, I, I, P, L, P, I, I, P, STREAM]),
     "fb_gemm_tc_grouped": (I, [P, L, P, L, I, P, I, P, I, L, I, I, I, I, P, STREAM]),
     "fb_gemm_tc_grouped_gated": (I, [P, L, P, L, I, P, I, P, I, L, I, I, I, I, P, STREAM]),
+    "fb_gemm_tc_act": (I, [P, L, P, L, P, I, L, I, I, I, I, P, STREAM]),
     "fb_gemm_tc_gated": (I, [P, L, P, L, P, I, L, I, I, I, I, P, L, P, I, P, STREAM]),
     # attention_simt.cu
-    "fb_paged_attention_simt": (I, [P, L, P, L, I, P, P, I, I, P, I, P, P, P, I, I, I, I, I, I, F, P, P, P, STREAM]),
+    "fb_paged_attention_simt": (I, [P, L, P, L, I, P, P, I, I, P, I, P, P, P, I, I, I, I, I, I, I, F, P, P, P, STREAM]),
     # qk_norm_rope.cu
     "fb_qk_norm_rope_kv_write": (I, [P, L, I, L, P, P, I, I, F, F, P, P, I, P, L, I, P, P, P, I, P, P, P, I, I, I, I, I,
                                      I, I, I, P, STREAM]),
@@ -58,8 +62,8 @@ _SIGNATURES = {
     # moe.cu
     "fb_moe_choose": (I, [P, L, I, L, P, I, I, I, I, I, P, P, P, I, F, STREAM]),
     "fb_moe_max_tiles": (I, [I, I, I]),
-    "fb_moe_gather_rows": (I, [P, L, I, P, P, I, I, STREAM]),
-    "fb_moe_sort": (I, [P, I, I, I, I, I, P, P, P, STREAM]),
+    "fb_moe_gather_rows": (I, [P, L, I, P, P, I, I, P, P, STREAM]),
+    "fb_moe_sort": (I, [P, I, I, I, I, I, P, P, P, P, STREAM]),
     "fb_moe_combine": (I, [P, L, P, P, I, P, I, L, P, P, I, I, P, I, L, STREAM]),
     # layer_norm.cu
     "fb_add_layernorm": (I, [P, P, I, L, P, I, P, I, P, I, I, F, STREAM]),
@@ -70,8 +74,8 @@ _SIGNATURES = {
     "fb_gla_prepare": (I, [P, L, I, L, P, P, I, I, F, F, P, P, I, I, I, I, STREAM]),
     "fb_gla_recurrent": (I, [P, P, P, L, P, P, P, I, I, P, I, I, I, STREAM]),
     # latent_attention.cu
-    "fb_mla_latents": (I, [P, L, I, L, I, P, P, I, I, I, P, I, F, P, P, I, P, P, P, I, P, P, I, I, I, I, P, STREAM]),
-    "fb_head_linear": (I, [P, I, L, L, I, L, P, I, P, I, L, L, P, L, I, L, I, P, P, I, I, I, I, I, I, STREAM]),
+    "fb_mla_latents": (I, [P, L, I, L, I, P, P, I, I, I, P, I, F, P, P, I, I, P, P, P, I, P, P, I, I, I, I, P, STREAM]),
+    "fb_head_linear": (I, [P, I, L, L, I, L, P, I, P, I, L, L, P, L, I, L, I, P, P, I, I, I, I, I, I, I, STREAM]),
     "fb_rope_neighbours": (I, [P, L, P, P, I, I, I, I, STREAM]),
     # diff_attention.cu
     "fb_qkv_bias_cache_write": (I, [P, L, I, L, P, I, P, L, I, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, I, P,
@@ -84,8 +88,8 @@ _SIGNATURES = {
     "fb_diff_attention_mma": (I, [P, L, P, L, P, P, P, I, I, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, F, F, F, F, I,
                                   P, L, P, STREAM]),
     # attention_mma.cu
-    "fb_paged_attention_mma": (I, [P, L, P, L, P, P, I, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, P, P, I, P, L,
-                                   P, L, L, I, P, STREAM]),
+    "fb_paged_attention_mma": (I, [P, L, P, L, P, P, I, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, P, P, I, P,
+                                   L, P, L, L, I, P, STREAM]),
     # sampling.cu
     "fb_apply_penalties": (I, [P, L, I, P, P, P, P, P, P, I, STREAM]),
     "fb_apply_logit_bias": (I, [P, L, I, P, P, P, I, STREAM]),

@@ -375,11 +375,12 @@ def _slopes(score_slopes, nh: int) -> int:
 
 def paged_attention_simt(q, out, k_pool, v_pool, block_table, positions, row_seq, nh: int, nkv: int, hd: int,
                          window: int, scale: float, status, table_base=None, score_slopes=None, sinks=None,
-                         vd: int = 0) -> None:
+                         vd: int = 0, keep_first: int = 0) -> None:
     """score_slopes (float32 per query head, optional): slope * (key position - query position) is added to every
     scaled score, a linear penalty on distance.  sinks (float32 per query head, optional): one more softmax slot per
     head whose score is that number, unscaled, and which has no value.  vd: the size of a value row where it is not
-    the key row's (the output then has nh * vd columns)."""
+    the key row's (the output then has nh * vd columns).  keep_first: under a window, the keys at positions below
+    this stay visible to every later query."""
     _cuda(q, out, k_pool, v_pool, block_table, positions, row_seq, status, table_base, sinks)
     _i32(table_base, "table_base")
     n = q.shape[0]
@@ -397,8 +398,8 @@ def paged_attention_simt(q, out, k_pool, v_pool, block_table, positions, row_seq
     check(lib().fb_paged_attention_simt(
         q.data_ptr(), _rows(q), out.data_ptr(), _rows(out), dtype_code(q), k_pool.data_ptr(), v_pool.data_ptr(),
         page_size, n_pages, block_table.data_ptr(), block_table.stride(0), _ptr(table_base), positions.data_ptr(),
-        row_seq.data_ptr(), n, nh, nkv, hd, vd, int(window), float(scale), _slopes(score_slopes, nh), _ptr(sinks),
-        status.data_ptr(), _stream()), "paged_attention_simt")
+        row_seq.data_ptr(), n, nh, nkv, hd, vd, int(window), int(keep_first), float(scale), _slopes(score_slopes, nh),
+        _ptr(sinks), status.data_ptr(), _stream()), "paged_attention_simt")
 
 
 def apply_penalties(logits, rows, tokens, counts, repetition, presence, frequency) -> None:
@@ -521,6 +522,18 @@ def gemm_tc_gated(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: t
                                  _stream()), "gemm_tc_gated", (M, N, K))
 
 
+def gemm_tc_act(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.Tensor, activation_name: str) -> None:
+    """out[M, N] = act(a @ w^T) with a plain activation (PLAIN_ACTIVATIONS) in the product's epilogue."""
+    _cuda(a, w, out, status)
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape[0] != M or out.shape[1] != N:
+        raise KernelError(f"gemm: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)} do not agree")
+    check(lib().fb_gemm_tc_act(a.data_ptr(), _rows(a), w.data_ptr(), _rows(w), out.data_ptr(), dtype_code(out),
+                               _rows(out), M, N, K, plain_activation_code(activation_name), status.data_ptr(),
+                               _stream()), "gemm_tc_act", (M, N, K))
+
+
 def linear_slabs(a: torch.Tensor, w: torch.Tensor, slabs: torch.Tensor, ctx) -> int:
     """slabs[0] + ... + slabs[k-1] = a @ w^T; returns k.  The tensor-core kernel leaves the split-K shares for the
     next kernel to add; every other path writes the whole product into slabs[0]."""
@@ -553,15 +566,19 @@ def grouped_tile(pairs: int, groups: int, tensor_cores: bool) -> int:
     return 64
 
 
-def gather_rows(h: torch.Tensor, place_token: torch.Tensor, out: torch.Tensor) -> None:
-    """out[i] = h[place_token[i]], zeros where place_token[i] < 0."""
-    _cuda(h, place_token, out)
+def gather_rows(h: torch.Tensor, place_token: torch.Tensor, out: torch.Tensor, share=None, place_pair=None) -> None:
+    """out[i] = h[place_token[i]], zeros where place_token[i] < 0.  With share (float32, one per (token, choice) pair)
+    and place_pair (the pair of every place): out[i] = share[place_pair[i]] * h[place_token[i]]."""
+    _cuda(h, place_token, out, share, place_pair)
     _i32(place_token, "place_token")
+    _i32(place_pair, "place_pair")
+    if (share is None) != (place_pair is None) or (share is not None and share.dtype != torch.float32):
+        raise KernelError("gather_rows: float32 shares come with the pair of every place")
     rows, D = out.shape
     if h.dtype != out.dtype or h.shape[1] != D or not out.is_contiguous() or place_token.numel() < rows:
         raise KernelError("gather_rows: shapes or dtypes do not agree")
     check(lib().fb_moe_gather_rows(h.data_ptr(), _rows(h), dtype_code(h), place_token.data_ptr(), out.data_ptr(), rows,
-                                   D, _stream()), "moe_gather_rows")
+                                   D, _ptr(share), _ptr(place_pair), _stream()), "moe_gather_rows")
 
 
 def gemm_tc_grouped(a: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, tile: int, out: torch.Tensor,
@@ -596,28 +613,33 @@ def gemm_tc_grouped_gated(a: torch.Tensor, w: torch.Tensor, tile_group: torch.Te
 
 
 def grouped_gated_linear(a: torch.Tensor, row_index, w: torch.Tensor, tile_group: torch.Tensor, tile: int,
-                         out: torch.Tensor, activation: str, ctx) -> None:
+                         out: torch.Tensor, activation: str, ctx, row_share=None, row_pair=None) -> None:
     """out[m] = act(gate) * up of a[row_index[m]] under the weights of the row tile's group (w [groups, 2 I, K], gate
     and up rows alternating): on the tcgen05 kernel with the activation in its epilogue for bfloat16 operands, else
-    the float32-FMA grouped product followed by the activation kernel."""
+    the float32-FMA grouped product followed by the activation kernel.  row_share / row_pair (with row_index): the
+    fetched row is multiplied by row_share[row_pair[m]] on its way (see gather_rows)."""
     if grouped_tc_supported(a, w, out):
         with ctx.ws.scope():
             side = a
             if row_index is not None:
                 side = ctx.ws.alloc((out.shape[0], a.shape[1]), a.dtype)
-                gather_rows(a, row_index, side)
+                gather_rows(a, row_index, side, row_share, row_pair)
             gemm_tc_grouped_gated(side, w, tile_group, tile, out, ctx.runtime.status, activation)
         return
     if tile not in (16, 64):
         raise KernelError(f"grouped gemm: the float32-FMA kernel takes tiles of 16 or 64 rows, not {tile}")
     with ctx.ws.scope():
+        if row_share is not None:           # the scaled rows side by side first; the product then reads them in order
+            side = ctx.ws.alloc((out.shape[0], a.shape[1]), a.dtype)
+            gather_rows(a, row_index, side, row_share, row_pair)
+            a, row_index = side, None
         gu = ctx.ws.alloc((out.shape[0], w.shape[1]), torch.float32)
         gemm_simt_grouped(a, row_index, w, tile_group, tile, gu, None)
         gate_mul(gu, out, activation=activation)
 
 
 def grouped_linear(a: torch.Tensor, row_index, w: torch.Tensor, tile_group: torch.Tensor, tile: int,
-                   out: torch.Tensor, activation_name=None, ctx=None) -> None:
+                   out: torch.Tensor, activation_name=None, ctx=None, row_share=None, row_pair=None) -> None:
     """out[m] = act(a[row_index[m]] @ w[tile_group[m // tile]]^T) with w [groups, N, K]: the product of routed
     experts over rows that were sorted by expert and padded to whole tiles.  bfloat16 operands go to the tcgen05
     kernel (rows that have to be fetched through row_index are first laid side by side, since tensor-map copies
@@ -626,13 +648,21 @@ def grouped_linear(a: torch.Tensor, row_index, w: torch.Tensor, tile_group: torc
         if row_index is not None:
             with ctx.ws.scope():
                 side = ctx.ws.alloc((out.shape[0], a.shape[1]), a.dtype)
-                gather_rows(a, row_index, side)
+                gather_rows(a, row_index, side, row_share, row_pair)
                 gemm_tc_grouped(side, w, tile_group, tile, out, ctx.runtime.status, activation_name)
         else:
             gemm_tc_grouped(a, w, tile_group, tile, out, ctx.runtime.status, activation_name)
         return
     if tile not in (16, 64):
         raise KernelError(f"grouped gemm: the float32-FMA kernel takes tiles of 16 or 64 rows, not {tile}")
+    if row_share is not None:
+        if ctx is None:
+            raise KernelError("grouped gemm: rows scaled on their way need the step's scratch (ctx)")
+        with ctx.ws.scope():
+            side = ctx.ws.alloc((out.shape[0], a.shape[1]), a.dtype)
+            gather_rows(a, row_index, side, row_share, row_pair)
+            gemm_simt_grouped(side, None, w, tile_group, tile, out, activation_name)
+        return
     gemm_simt_grouped(a, row_index, w, tile_group, tile, out, activation_name)
 
 
@@ -706,7 +736,7 @@ def paged_attention_mma(q, out, k_pool, v_pool, block_table, seq_q_start, seq_q_
                         max_q_len: int, max_kv_len: int, any_short: bool, any_long: bool, nh: int, nkv: int,
                         hd: int, window: int, scale: float, status, table_base=None, prefetch=None,
                         multi_seqs=None, n_multi: int = 0, score_slopes=None, sinks=None,
-                        weights_float32: bool = False) -> None:
+                        weights_float32: bool = False, keep_first: int = 0) -> None:
     """bfloat16 attention on the tensor cores over the paged cache; sequences are described per entry of the
     step (first row, rows, first position).  any_short / any_long say whether the step holds sequences with
     rows * (nh/nkv) <= 16 / > 16 (attention_is_short), which run in different arrangements of the kernel.  table_base (int32 per
@@ -718,7 +748,9 @@ def paged_attention_mma(q, out, k_pool, v_pool, block_table, seq_q_start, seq_q_
     query head, optional): one more softmax slot per head, its score that number unscaled, without key or value.
     weights_float32: the softmax weights enter P V as two bfloat16 numbers each (the rounded weight and what the
     rounding left: 16 bits of mantissa, two MMAs for one) instead of rounded to bfloat16; portions then run on the
-    mma.sync kernel, whose weights are in registers."""
+    mma.sync kernel, whose weights are in registers.  keep_first: under a window, the keys at positions below this
+    stay visible to every later query (their tiles are walked ahead of the window's; portions then run on the
+    mma.sync kernel)."""
     _cuda(q, out, k_pool, v_pool, block_table, seq_q_start, seq_q_len, seq_pos_start, status, table_base, multi_seqs,
           sinks)
     if sinks is not None and (sinks.dtype != torch.float32 or sinks.numel() != nh or not sinks.is_contiguous()):
@@ -738,7 +770,7 @@ def paged_attention_mma(q, out, k_pool, v_pool, block_table, seq_q_start, seq_q_
         block_table.data_ptr(), block_table.stride(0), _ptr(table_base), seq_q_start.data_ptr(),
         seq_q_len.data_ptr(), seq_pos_start.data_ptr(), _ptr(multi_seqs), int(n_multi), n_seqs, max_q_len, max_kv_len,
         1 if any_short else 0,
-        1 if any_long else 0, nh, nkv, hd, int(window), float(scale), _slopes(score_slopes, nh), _ptr(sinks),
+        1 if any_long else 0, nh, nkv, hd, int(window), int(keep_first), float(scale), _slopes(score_slopes, nh), _ptr(sinks),
         1 if weights_float32 else 0, scratch.data_ptr(), scratch.numel(),
         *prefetch_arguments(prefetch), status.data_ptr(), _stream()), "paged_attention_mma")
 
@@ -759,7 +791,8 @@ def attention_is_short(q_len: int, nh: int, nkv: int) -> bool:
 
 
 def paged_attention(ctx, q, out, cache, nh: int, nkv: int, hd: int, window: int, scale: float,
-                    next_weight=None, score_slopes=None, sinks=None, vd: int = 0, weights_float32: bool = False) -> None:
+                    next_weight=None, score_slopes=None, sinks=None, vd: int = 0, weights_float32: bool = False,
+                    keep_first: int = 0) -> None:
     """Attention of every row of the step over its request's cached keys: the tensor-core kernel for bfloat16
     and head sizes it takes, the float32 CUDA-core kernel otherwise (all of the 32-bit mode).  next_weight: the
     matrix of the product that follows, whose start the bfloat16 kernel may fetch into L2 (a hint)."""
@@ -771,11 +804,12 @@ def paged_attention(ctx, q, out, cache, nh: int, nkv: int, hd: int, window: int,
                             b.seq_pos_start_d, b.n_seqs, b.max_q_len, b.max_kv_len, any(short), not all(short),
                             nh, nkv, hd, window, scale, ctx.runtime.status, table_base=cache.table_base,
                             prefetch=next_weight, multi_seqs=b.multi_seqs_d, n_multi=b.n_multi,
-                            score_slopes=score_slopes, sinks=sinks, weights_float32=weights_float32)
+                            score_slopes=score_slopes, sinks=sinks, weights_float32=weights_float32,
+                            keep_first=keep_first)
     else:
         paged_attention_simt(q, out, cache.k_pool, cache.v_pool, cache.block_table, b.positions, b.row_seq,
                              nh, nkv, hd, window, scale, ctx.runtime.status, table_base=cache.table_base,
-                             score_slopes=score_slopes, sinks=sinks, vd=vd)
+                             score_slopes=score_slopes, sinks=sinks, vd=vd, keep_first=keep_first)
 
 
 def diff_attention_mma_supported(q: torch.Tensor, nh: int, nkv: int, kd: int, vd: int) -> bool:
@@ -943,7 +977,7 @@ def gdr_out_norm(o, proj, gate_off: int, weight, eps: float, out, H: int, dv: in
 # ---------------------------------------------------------------------------
 # routed experts
 # ---------------------------------------------------------------------------
-ROUTER_RULES = {"softmax_of_chosen": 0, "softmax_of_all": 1}
+ROUTER_RULES = {"softmax_of_chosen": 0, "softmax_of_all": 1, "sigmoid": 2}
 
 
 def moe_choose(z, bias, gate_col: int, experts: int, top: int, chosen, share, gate, n_partials: int = 1,
@@ -951,7 +985,8 @@ def moe_choose(z, bias, gate_col: int, experts: int, top: int, chosen, share, ga
     """Per token: the `top` experts with the largest logits z[:, :experts] + bias (float32; z possibly split-K
     shares), their softmax weights, and (gate_col >= 0) gate = sigmoid(z[:, gate_col]).  rule 'softmax_of_all':
     scores = softmax(z) over all experts, the `top` largest of score + bias are chosen, and the weights are the chosen
-    scores over their sum, times `weight_scale`."""
+    scores over their sum, times `weight_scale`.  rule 'sigmoid': scores = sigmoid of every logit by itself, the `top`
+    largest of score + bias are chosen, and the weights are the chosen scores as they are, times `weight_scale`."""
     if rule not in ROUTER_RULES:
         raise KernelError(f"router: rule '{rule}' is not one of {sorted(ROUTER_RULES)}")
     _cuda(z, bias, chosen, share, gate)
@@ -969,30 +1004,34 @@ def moe_max_tiles(pairs: int, experts: int, tile: int) -> int:
     return pairs // tile + min(experts, pairs)
 
 
-def moe_sort(chosen, experts: int, tile: int, place_token, pair_place, tile_expert) -> None:
-    """The (token, choice) pairs in expert order, every expert's stretch padded to whole row tiles."""
-    _cuda(chosen, place_token, pair_place, tile_expert)
+def moe_sort(chosen, experts: int, tile: int, place_token, pair_place, tile_expert, place_pair=None) -> None:
+    """The (token, choice) pairs in expert order, every expert's stretch padded to whole row tiles.  place_pair
+    (int32 [places], optional) receives, for every place that holds a token, the pair it stands for."""
+    _cuda(chosen, place_token, pair_place, tile_expert, place_pair)
+    _i32(place_pair, "place_pair")
     n, K = chosen.shape
+    if place_pair is not None and place_pair.numel() < place_token.numel():
+        raise KernelError("moe_sort: place_pair is shorter than place_token")
     check(lib().fb_moe_sort(chosen.data_ptr(), n * K, K, int(experts), int(tile), tile_expert.numel(),
-                            place_token.data_ptr(), pair_place.data_ptr(), tile_expert.data_ptr(), _stream()),
-          "moe_sort")
+                            place_token.data_ptr(), pair_place.data_ptr(), tile_expert.data_ptr(), _ptr(place_pair),
+                            _stream()), "moe_sort")
 
 
 def moe_combine(expert_out, pair_place, share, shared_out, shared_partials: int, shared_partial_stride: int, gate,
                 out, n: int, pass_on=None) -> None:
     """out[t] = sum_k share[t, k] * expert_out[pair_place[t, k]] + gate[t] * sum of shared_out's shares (gate None:
     1).  pass_on ([n, D], optional): a pair without a place (an expert that has no weights) contributes
-    share * pass_on[t]."""
+    share * pass_on[t].  share None: every pair counts once (experts whose share scaled what they read)."""
     _cuda(expert_out, pair_place, share, shared_out, gate, out, pass_on)
     if pass_on is not None and pass_on.shape[1] != out.shape[1]:
         raise KernelError("moe_combine: the rows handed on must have the output's width")
     D = out.shape[1]
-    K = share.shape[1]
+    K = pair_place.shape[1]
     if expert_out.dtype != torch.float32 or out.dtype != torch.float32 or not out.is_contiguous() \
             or expert_out.shape[1] != D or (shared_out is not None and (shared_out.dtype != torch.float32
                                                                         or not shared_out.is_contiguous())):
         raise KernelError("moe_combine: float32 rows of the output's width wanted")
-    check(lib().fb_moe_combine(expert_out.data_ptr(), _rows(expert_out), pair_place.data_ptr(), share.data_ptr(), K,
+    check(lib().fb_moe_combine(expert_out.data_ptr(), _rows(expert_out), pair_place.data_ptr(), _ptr(share), K,
                                _ptr(shared_out), int(shared_partials), int(shared_partial_stride), _ptr(gate),
                                out.data_ptr(), int(n), D, _ptr(pass_on),
                                dtype_code(pass_on) if pass_on is not None else 0,
@@ -1101,8 +1140,12 @@ def gla_recurrent(qkv, decay, state, batch, o, H: int, dk: int, dv: int) -> None
 # ---------------------------------------------------------------------------
 # latent attention
 # ---------------------------------------------------------------------------
+ROTARY_PAIRING = {"neighbours": 0, "halves": 1}      # which dimensions form pair i: (2i, 2i + 1) or (i, i + half)
+
+
 def mla_latents(proj, Rq: int, wq, cq, kv_off: int, Rc: int, r: int, wkv, eps: float, cos, sin, half: int, cache,
-                positions, row_seq, status, n_partials: int = 1, partial_stride: int = 0) -> None:
+                positions, row_seq, status, n_partials: int = 1, partial_stride: int = 0,
+                pairing: str = "neighbours") -> None:
     """cq = rmsnorm(proj[:, :Rq]) * wq; with a writable cache also the token's cache row [rmsnorm(proj[:, kv_off:
     kv_off + Rc]) * wkv | rot(proj[:, kv_off + Rc : kv_off + Rc + r])] (csrc/latent_attention.cu)."""
     _cuda(proj, wq, cq, wkv, cos, sin, positions, row_seq, status)
@@ -1116,7 +1159,8 @@ def mla_latents(proj, Rq: int, wq, cq, kv_off: int, Rc: int, r: int, wkv, eps: f
             raise KernelError("latent attention: the cache rows do not fit the latent")
     check(lib().fb_mla_latents(
         proj.data_ptr(), _rows(proj), int(n_partials), int(partial_stride), Rq, wq.data_ptr(), cq.data_ptr(), kv_off,
-        Rc, r, _ptr(wkv), dtype_code(wq), float(eps), _ptr(cos), _ptr(sin), half, _ptr(positions), _ptr(row_seq),
+        Rc, r, _ptr(wkv), dtype_code(wq), float(eps), _ptr(cos), _ptr(sin), half, ROTARY_PAIRING[pairing],
+        _ptr(positions), _ptr(row_seq),
         _ptr(cache.block_table) if pool is not None else 0, cache.block_table.stride(0) if pool is not None else 0,
         _ptr(cache.table_base) if pool is not None else 0, _ptr(pool), dtype_code(cq),
         cache.page_size if pool is not None else 1, pool.shape[0] if pool is not None else 0, n, status.data_ptr(),
@@ -1125,11 +1169,12 @@ def mla_latents(proj, Rq: int, wq, cq, kv_off: int, Rc: int, r: int, wkv, eps: f
 
 def head_linear(a, a_head: int, w, out, o_head: int, n: int, n_partials: int = 1, partial_stride: int = 0, gate=None,
                 gate_off: int = 0, gate_partials: int = 1, gate_partial_stride: int = 0, cos=None, sin=None,
-                half: int = 0, rot: int = 0) -> None:
+                half: int = 0, rot: int = 0, pairing: str = "neighbours") -> None:
     """out[t, h*o_head + c] = sum_k w[h, c, k] * a[t, h*a_head + k] for every head h (w [H, N, K]); `a` may be the
     first of float32 shares.  gate (float32 rows, possibly shares): the result is multiplied by
     sigmoid(gate[t, gate_off + h*N + c]).  rot > 0: columns K .. K+rot of a's head go, their first 2*half dimensions
-    turned pairwise by (cos, sin), to columns N .. N+rot of out's head."""
+    turned pairwise by (cos, sin), to columns N .. N+rot of out's head; `pairing` says which dimensions form a pair
+    (ROTARY_PAIRING)."""
     _cuda(a, w, out, gate, cos, sin)
     H, N, K = w.shape
     if not w.is_contiguous() or a.shape[0] < n or out.shape[0] < n:
@@ -1138,7 +1183,7 @@ def head_linear(a, a_head: int, w, out, o_head: int, n: int, n_partials: int = 1
                                w.data_ptr(), dtype_code(w), out.data_ptr(), dtype_code(out), _rows(out), int(o_head),
                                _ptr(gate), _rows(gate) if gate is not None else 0, int(gate_partials),
                                int(gate_partial_stride), int(gate_off), _ptr(cos), _ptr(sin), int(half), int(rot),
-                               int(n), H, N, K, _stream()), "head_linear", (n * H, N, K))
+                               ROTARY_PAIRING[pairing], int(n), H, N, K, _stream()), "head_linear", (n * H, N, K))
 
 
 def rope_neighbours(x, cos, sin, half: int, heads: int, head_dim: int) -> None:
@@ -1149,3 +1194,47 @@ def rope_neighbours(x, cos, sin, half: int, heads: int, head_dim: int) -> None:
         raise KernelError("rope_neighbours: float32 rows of heads * head_dim wanted")
     check(lib().fb_rope_neighbours(x.data_ptr(), _rows(x), cos.data_ptr(), sin.data_ptr(), int(half), int(heads),
                                    int(head_dim), x.shape[0], _stream()), "rope_neighbours")
+
+
+# ---------------------------------------------------------------------------
+# an output gate on a mixer's heads; several residual streams
+# ---------------------------------------------------------------------------
+def sigmoid_gate(a: torch.Tensor, gate: torch.Tensor, n: int, n_partials: int = 1, partial_stride: int = 0) -> None:
+    """a[t, c] *= sigmoid(sum of the shares of gate[t, c]) in place for the first n rows; gate is a float32 view
+    [n, width of a] (columns of a wider product as a rule), the first of n_partials shares."""
+    _cuda(a, gate)
+    if gate.dtype != torch.float32 or gate.shape[1] != a.shape[1] or a.shape[0] < n or gate.shape[0] < n:
+        raise KernelError("sigmoid_gate: float32 gate columns of the rows' width wanted")
+    check(lib().fb_sigmoid_gate(a.data_ptr(), _rows(a), dtype_code(a), gate.data_ptr(), _rows(gate), int(n_partials),
+                                int(partial_stride), int(n), a.shape[1], _stream()), "sigmoid_gate")
+
+
+def hc_step(streams: torch.Tensor, y, n_partials: int, partial_stride: int, mix, out_w, in_w, norm_weight, eps: float,
+            weight_offset: float, out, n: int, rows=None, write_back: bool = True) -> None:
+    """One pass over the residual streams (float32 [S, n_all, D]) between two sublayers: with y (float32 [n, D], the
+    first of n_partials shares) every stream becomes sum_s mix[s, t] x_s + out_w[t] y (written back unless told
+    otherwise); then u = sum_t in_w[t] x_t (in_w None: ones) and out = rmsnorm(u) * (norm_weight + weight_offset), or
+    u itself (float32) where norm_weight is None; out None: only the write.  rows (int32, optional): only those rows
+    are formed, nothing is written back.  mix [S, S] ([from, to]), out_w [S], in_w [S]: float32."""
+    _cuda(streams, y, mix, out_w, in_w, norm_weight, out, rows)
+    _i32(rows, "rows")
+    S, n_all, D = streams.shape
+    for t in (mix, out_w, in_w):
+        if t is not None and (t.dtype != torch.float32 or not t.is_contiguous()):
+            raise KernelError("hc_step: the streams' weights are contiguous float32")
+    if streams.dtype != torch.float32 or streams.stride(2) != 1 or streams.stride(1) != D \
+            or (y is not None and (y.dtype != torch.float32 or not y.is_contiguous() or y.shape[-1] != D)) \
+            or (mix is not None and mix.numel() != S * S) or (out_w is not None and out_w.numel() != S) \
+            or (in_w is not None and in_w.numel() != S) or (norm_weight is not None and norm_weight.numel() != D):
+        raise KernelError("hc_step: bad shapes")
+    n_out = rows.numel() if rows is not None else int(n)
+    if out is not None and (not out.is_contiguous() or out.shape[-1] != D or out.shape[0] < n_out
+                            or (norm_weight is None and out.dtype != torch.float32)):
+        raise KernelError("hc_step: the output is contiguous rows of the streams' width (float32 without a norm)")
+    if rows is not None:
+        write_back = False
+    check(lib().fb_hc_step(streams.data_ptr(), streams.stride(0), S, _ptr(y), int(n_partials), int(partial_stride),
+                           _ptr(mix), _ptr(out_w), _ptr(in_w), _ptr(norm_weight),
+                           dtype_code(norm_weight) if norm_weight is not None else 0, float(eps), float(weight_offset),
+                           _ptr(out), dtype_code(out) if out is not None else 0, _ptr(rows), 1 if write_back else 0,
+                           n_out, D, _stream()), "hc_step")

@@ -1,3 +1,3 @@
 """Architectures: import the built-in ones so that they are registered."""
-from . import fegizen, mistral, nodepel, zedivik  # noqa: F401
+from . import fegizen, mistral, nodepel, tubepel, zedivik  # noqa: F401
 from .decoder import DecoderModel  # noqa: F401

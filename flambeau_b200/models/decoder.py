@@ -88,6 +88,7 @@ class DecoderModel:
             self.layers[call.layer].forward(ctx, stream, ci)
         if b.n_out == 0:
             return None
+        stream.close(ctx)         # (a block arrangement that kept the stream as several copies folds them into one)
         h = ctx.step_alloc((b.n_out, self.hidden_size), rt.dtype)
         self.final_norm.add_norm(ctx, stream.x, stream.pending, h, rows=b.out_rows[:b.n_out],
                                  n_partials=stream.pending_slabs, delta_norm=stream.pending_norm)

@@ -41,19 +41,25 @@ class PagedAttention(Mixer):
     in bfloat16 (two bfloat16 numbers a weight, two MMAs for one; the 32-bit mode has them in float32 anyway), for
     designs that say their attention weights are 32-bit numbers; otherwise they are rounded to bfloat16 for that
     product, as flash attention kernels do.
-    `names`: what the tensors are called behind the prefix (keys q, k, v, o, q_norm, k_norm, sink), for checkpoints
+    `keep_first` (with a window): the keys at positions below this stay visible to every later query, at their true
+    positions (for rotation and distances); a request's pages are then kept until it ends.
+    `gate` (bool): the heads' outputs are multiplied element by element by sigmoid(Wg h) before the output projection
+    (`<prefix><names.g>`, [num_heads * value_dim, width]; Wg reads the same input as the other projections and is
+    part of their one product).
+    `names`: what the tensors are called behind the prefix (keys q, k, v, o, q_norm, k_norm, sink, g), for checkpoints
     with other names than the defaults."""
     graph_safe = True
 
     DEFAULT_NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
-                     "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "sink": "sinks"}
+                     "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "sink": "sinks", "g": "g_proj.weight"}
 
     def __init__(self, runtime=None, prefix="", *, width: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  window: int = 0, position: PartSpec | None = None, scale: float | None = None,
                  init_std: float = 0.02, qk_norm: PartSpec | None = None, distance_slopes=None,
                  qk_norm_reach: str = "head", value_dim: int | None = None, sink: bool = False, names=None,
-                 weights_float32: bool = False):
+                 weights_float32: bool = False, keep_first: int = 0, gate: bool = False):
         super().__init__(runtime, prefix)
+        self.gate = bool(gate)
         self.width, self.nh, self.nkv, self.hd = int(width), int(num_heads), int(num_kv_heads), int(head_dim)
         self.vd = int(value_dim) if value_dim else self.hd
         self.sink = bool(sink)
@@ -66,6 +72,7 @@ class PagedAttention(Mixer):
         if self.nh % self.nkv:
             raise ValueError(f"{self.nh} query heads are not a multiple of {self.nkv} key/value heads")
         self.window = int(window or 0)
+        self.keep_first = int(keep_first or 0) if self.window else 0
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.hd)
         self.position = build_part(position, runtime) if position is not None else None
         self.q_norm = self.k_norm = None
@@ -97,7 +104,8 @@ class PagedAttention(Mixer):
         return [p for p in (self.position, self.q_norm, self.k_norm) if p is not None]
 
     def cache_requirement(self):
-        return KVRequirement(self.nkv, self.hd, self.window, v_head_dim=self.vd if self.vd != self.hd else 0)
+        return KVRequirement(self.nkv, self.hd, self.window, v_head_dim=self.vd if self.vd != self.hd else 0,
+                             keep_first=self.keep_first)
 
     def own_tensor_specs(self):
         p, init = self.prefix, ("normal", self.init_std)
@@ -110,11 +118,16 @@ class PagedAttention(Mixer):
         }
         if self.sink:
             specs[p + nm["sink"]] = TensorSpec((self.nh,), init=("normal", 1.0))
+        if self.gate:
+            specs[p + nm["g"]] = TensorSpec((self.nh * self.vd, self.width), init=init)
         return specs
 
     def own_bind(self, tensors):
         p, nm = self.prefix, self.names
         stack = [tensors[p + nm["q"]], tensors[p + nm["k"]], tensors[p + nm["v"]]]
+        self.gate_off = sum(t.shape[0] for t in stack)          # the gate's columns lie behind q, k and v
+        if self.gate:
+            stack.append(tensors[p + nm["g"]])
         rows = sum(t.shape[0] for t in stack)
         if rows % 8 and (self.q_norm is not None or self.vd != self.hd) and self._fused_norm_kernel():
             # rows of zeros up to a multiple of 8, so that the product's float32 rows stay 16-byte aligned
@@ -165,20 +178,26 @@ class PagedAttention(Mixer):
                 hint = self.o.weight if ctx.l2_hints and n <= 64 else None
                 ops.paged_attention(ctx, q, a, cache, self.nh, self.nkv, self.hd, self.window, self.scale,
                                     next_weight=hint, score_slopes=self.distance_slopes, sinks=self.sinks, vd=self.vd,
-                                    weights_float32=self.weights_float32)
+                                    weights_float32=self.weights_float32, keep_first=self.keep_first)
+                if self.gate:
+                    ops.sigmoid_gate(a, slabs[0][:, self.gate_off:self.gate_off + self.nh * self.vd], n, parts,
+                                     slabs.stride(0))
                 ctx.to_stream(self.o, a)
                 return
             if self.vd != self.hd or self.qk_norm_reach != "head":
                 raise ValueError("attention: value rows of their own width, or a norm over the whole projection, "
                                  "need the framework's RMS norm and a position encoding that hands out its tables")
+            if self.gate and self.q_norm is not None:
+                raise ValueError("attention: an output gate beside query/key norms needs the framework's RMS norm and a "
+                                 "position encoding that hands out its tables")
             if self.q_norm is None:
-                qkv_slabs = ctx.ws.alloc((ctx.max_slabs if fused else 1, n, self.qw + 2 * self.kvw), torch.float32)
+                qkv_slabs = ctx.ws.alloc((ctx.max_slabs if fused else 1, n, self.qkv.out_features), torch.float32)
                 parts = self.qkv.slabs(ctx, h, qkv_slabs)
                 stride = qkv_slabs.stride(0)
                 qkv = qkv_slabs[0]
                 q_in = qkv[:, :self.qw]
                 k = qkv[:, self.qw:self.qw + self.kvw]
-                v = qkv[:, self.qw + self.kvw:]
+                v = qkv[:, self.qw + self.kvw:self.qw + 2 * self.kvw]
             else:
                 # un-fused: three products from row slices of the stacked weight, so that the heads of q and of k
                 # lie as rows of their own; each head is normalised, then everything goes on as before
@@ -211,7 +230,9 @@ class PagedAttention(Mixer):
             hint = self.o.weight if ctx.l2_hints and n <= 64 else None
             ops.paged_attention(ctx, q, a, cache, self.nh, self.nkv, self.hd, self.window, self.scale,
                                 next_weight=hint, score_slopes=self.distance_slopes, sinks=self.sinks,
-                                weights_float32=self.weights_float32)
+                                weights_float32=self.weights_float32, keep_first=self.keep_first)
+            if self.gate:
+                ops.sigmoid_gate(a, qkv_slabs[0][:, self.gate_off:self.gate_off + self.qw], n, parts, stride)
             ctx.to_stream(self.o, a)
 
 

@@ -47,10 +47,18 @@ class KVRequirement:
     window: int = 0          # 0 = all earlier keys stay live; W > 0 = only the last W
     v_head_dim: int = 0      # elements of a value row where it differs from a key row (0: the same)
     values_in_keys: bool = False   # the key rows are the values as well: one pool serves as both, nothing is kept twice
+    keep_first: int = 0      # under a window: the first keys of a request stay visible to every later query
 
     @property
     def value_dim(self) -> int:
         return self.v_head_dim or self.head_dim
+
+    @property
+    def release_window(self) -> int:
+        """The window by which the cache manager gives pages back (0: never before the request ends).  A group whose
+        first keys stay visible keeps all its pages: a table row is one run of consecutive logical pages, and the
+        kept pages and the window's would be two."""
+        return 0 if self.keep_first > 0 else self.window
 
 
 @dataclass(frozen=True)

@@ -16,10 +16,19 @@ class ResidualStream:
     product, ctx.delta_slabs[0..k)), which the norm adds as well; 0 says that the
     part's last product has added its result to x itself (ctx.to_stream), so the
     norm has nothing to add.  `pending_norm` (a norm part, or None) says that the pending output passes through that
-    norm before it joins the stream; whoever adds the pending output applies it (Norm.add_norm(delta_norm=...))."""
+    norm before it joins the stream; whoever adds the pending output applies it (Norm.add_norm(delta_norm=...)).
+    `closer` (optional, set by a block arrangement that keeps the stream in another form, several copies of it, say):
+    close(ctx) calls it once after the last block, and it leaves the stream as one x with nothing pending."""
 
     def __init__(self, x, pending=None, pending_slabs: int = 1, pending_norm=None):
         self.x, self.pending, self.pending_slabs, self.pending_norm = x, pending, pending_slabs, pending_norm
+        self.closer = None
+
+    def close(self, ctx) -> None:
+        """After the last block: whatever form a block arrangement kept the stream in, it is one x again."""
+        if self.closer is not None:
+            closer, self.closer = self.closer, None
+            closer(ctx, self)
 
     def settle(self, ctx) -> None:
         """Add what is pending to x now (through the pending norm's kernel, which then normalises nothing else), for
@@ -219,6 +228,128 @@ class SandwichNormBlock(Part):
         stream.pending, stream.pending_slabs, stream.pending_norm = delta, ctx.pending_slabs, self.feed_forward_post_norm
 
 
+class HyperConnectionBlock(Part):
+    """A pre-norm layer on S copies of the residual stream (hyper-connections).  All copies start as the stream the
+    first such block finds.  Sublayer q (the mixer, then the feed-forward) with its learned weights in_q [S],
+    mix_q [S, S] (indexed [from, to]) and out_q [S]:
+
+        u = sum_s in_q[s] x_s;   y = sublayer(norm_q(u));   x_t <- sum_s mix_q[s, t] x_s + out_q[t] y   for all t at once
+
+    After the last block the stream is the sum of the copies.  The copies are float32 and live for the step
+    ([S, rows, width]); one kernel per sublayer does the write of the sublayer before it (whose output is left
+    pending, as split-K shares where its last product left them), this sublayer's read and its RMS norm; a norm of
+    another kind gets the read as float32 rows and normalises them itself.  No product adds to a stream by itself here
+    (ctx.stream_x stays None): what joins a copy is out_q[t] times the output.  `feed_forward` (with its norm) may be
+    None.  Tensors behind the prefix: `<names[0]>in`, `<names[0]>mix`, `<names[0]>out` for the mixer and the same
+    under names[1] for the feed-forward."""
+    graph_safe = True
+    category = "block"
+    STREAMS = "hyper_connections.streams"
+
+    def __init__(self, runtime=None, prefix="", *, streams: int, width: int, mixer: PartSpec, mixer_norm: PartSpec,
+                 feed_forward: PartSpec | None = None, feed_forward_norm: PartSpec | None = None,
+                 names=("hc1.", "hc2.")):
+        super().__init__(runtime, prefix)
+        self.S, self.width, self.names = int(streams), int(width), tuple(names)
+        if not 1 <= self.S <= 8:
+            raise ValueError(f"hyper-connections: {self.S} streams (1 to 8)")
+        self.mixer = build_part(mixer, runtime)
+        self.mixer_norm = build_part(mixer_norm, runtime)
+        self.feed_forward = self.feed_forward_norm = None
+        if feed_forward is not None:
+            if feed_forward_norm is None:
+                raise ValueError("a feed-forward behind a norm needs that norm")
+            self.feed_forward = build_part(feed_forward, runtime)
+            self.feed_forward_norm = build_part(feed_forward_norm, runtime)
+        self.weights = {}                   # (sublayer, 'in' | 'mix' | 'out') -> float32 tensor
+
+    def children(self):
+        return [p for p in (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward) if p is not None]
+
+    def _sublayers(self):
+        return self.names if self.feed_forward is not None else self.names[:1]
+
+    def own_tensor_specs(self):
+        # (close to one plain residual stream per copy: reads average the copies, writes reach every copy, the mix is
+        # near the identity, so that random weights still behave like a residual network)
+        specs = {}
+        for name in self._sublayers():
+            p = self.prefix + name
+            specs[p + "in"] = TensorSpec((self.S,), init=("normal_around", 1.0 / self.S, 0.1))
+            specs[p + "out"] = TensorSpec((self.S,), init=("normal_around", 1.0, 0.1))
+            specs[p + "mix"] = TensorSpec((self.S, self.S), init=("identity_plus_normal", 0.1))
+        return specs
+
+    def own_bind(self, tensors):
+        for name in self._sublayers():
+            for leaf in ("in", "mix", "out"):
+                self.weights[(name, leaf)] = tensors[self.prefix + name + leaf].float().contiguous()   # float32 in both modes
+
+    def own_weights(self):
+        return list(self.weights.values())
+
+    def _read(self, ctx, xs, stream, name, norm, h):
+        """The pending output joins the copies, then h = norm(sum_s in[s] x_s)."""
+        from .norms import RMSNorm
+        n = ctx.n_tokens
+        y, parts, written_by = stream.pending, stream.pending_slabs, getattr(stream, "pending_writer", None)
+        if y is None or written_by is None:
+            y, mix, out_w = None, None, None
+        else:
+            mix, out_w = written_by
+        stride = ctx.delta_slabs.stride(0) if parts > 1 else 0
+        in_w = self.weights[(name, "in")]
+        if type(norm) is RMSNorm:
+            ops.hc_step(xs, y, parts, stride, mix, out_w, in_w, norm.weight, norm.eps, norm.weight_offset, h, n)
+        else:
+            with ctx.ws.scope():
+                u = ctx.ws.alloc((n, self.width), torch.float32)
+                ops.hc_step(xs, y, parts, stride, mix, out_w, in_w, None, 0.0, 0.0, u, n)
+                norm.normalize(ctx, u, h)
+        stream.pending, stream.pending_slabs, stream.pending_writer = None, 0, None
+
+    def _leave(self, ctx, stream, name, delta):
+        stream.pending, stream.pending_slabs = delta, ctx.pending_slabs
+        stream.pending_writer = (self.weights[(name, "mix")], self.weights[(name, "out")])
+
+    @classmethod
+    def _close(cls, ctx, stream):
+        """x = the sum of the copies, the last sublayer's output written into them first."""
+        xs = ctx.shared.pop(cls.STREAMS)
+        y, parts, writer = stream.pending, stream.pending_slabs, getattr(stream, "pending_writer", None)
+        mix, out_w = writer if (y is not None and writer is not None) else (None, None)
+        if mix is None:
+            y = None
+        stride = ctx.delta_slabs.stride(0) if parts > 1 else 0
+        ops.hc_step(xs, y, parts, stride, mix, out_w, None, None, 0.0, 0.0, stream.x, ctx.n_tokens, write_back=False)
+        stream.pending, stream.pending_slabs, stream.pending_norm, stream.pending_writer = None, 0, None, None
+
+    def forward(self, ctx, stream: ResidualStream, call) -> None:
+        n = ctx.n_tokens
+        xs = ctx.shared.get(self.STREAMS)
+        if xs is None:
+            # the first block of a step that keeps copies: every copy starts as the stream it finds
+            stream.settle(ctx)
+            xs = ctx.shared[self.STREAMS] = ctx.step_alloc((self.S, n, self.width), torch.float32)
+            xs.copy_(stream.x[:n].unsqueeze(0).expand(self.S, n, self.width))
+            stream.closer = HyperConnectionBlock._close
+            stream.pending_writer = None
+        elif xs.shape[0] != self.S:
+            raise ValueError(f"hyper-connections: this block keeps {self.S} copies of the stream, the step has {xs.shape[0]}")
+        h, delta = ctx.normed, ctx.delta
+        ctx.stream_x = None
+        self._read(ctx, xs, stream, self.names[0], self.mixer_norm, h)
+        ctx.pending_slabs = 1
+        self.mixer.forward(ctx, h, delta, call)
+        self._leave(ctx, stream, self.names[0], delta)
+        if self.feed_forward is not None:
+            self._read(ctx, xs, stream, self.names[1], self.feed_forward_norm, h)
+            ctx.pending_slabs = 1
+            self.feed_forward.forward(ctx, h, delta)
+            self._leave(ctx, stream, self.names[1], delta)
+
+
 register_part("block", "pre_norm", PreNormBlock)
+register_part("block", "hyper_connections", HyperConnectionBlock)
 register_part("block", "sandwich_norm", SandwichNormBlock)
 register_part("block", "depth_averaged", DepthAveragedBlock)

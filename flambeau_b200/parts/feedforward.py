@@ -1,4 +1,4 @@
-"""Gated dense feed-forward (SiLU-gated in the architecture built here)."""
+"""Dense feed-forwards: gated (SiLU-gated in the architecture built here), and plain (one map, an activation, one map)."""
 from __future__ import annotations
 
 import os
@@ -82,4 +82,51 @@ class GatedMLP(FeedForward):
             ctx.to_stream(self.down, a)
 
 
+class PlainMLP(FeedForward):
+    """d = act(h Wu^T) Wd^T: no gate, no bias, no routing.  `activation` names one of the kernels' plain activations
+    (kernels.ops.PLAIN_ACTIVATIONS: relu_squared, silu, gelu_tanh).  Over a prompt's portion the activation runs in
+    the first product's epilogue; with few rows the product leaves float32 split-K shares and the activation kernel
+    adds them.  `names`: what the up and down tensors are called behind the prefix."""
+    graph_safe = True
+
+    def __init__(self, runtime=None, prefix="", *, width: int, inner: int, activation: str = "relu_squared",
+                 init_std: float = 0.02, names=("up", "down")):
+        super().__init__(runtime, prefix)
+        self.names = tuple(names)
+        if len(self.names) != 2:
+            raise ValueError("plain feed-forward: two tensor names wanted (up, down)")
+        if activation not in ops.PLAIN_ACTIVATIONS or not ops.PLAIN_ACTIVATIONS[activation]:
+            raise ValueError(f"plain feed-forward: activation '{activation}' is not implemented")
+        self.activation = activation
+        self.width, self.inner, self.init_std = int(width), int(inner), init_std
+        self.up = self.down = None
+
+    def own_tensor_specs(self):
+        p, init = self.prefix, ("normal", self.init_std)
+        up, down = self.names
+        return {p + up: TensorSpec((self.inner, self.width), init=init),
+                p + down: TensorSpec((self.width, self.inner), init=init)}
+
+    def own_bind(self, tensors):
+        up, down = self.names
+        self.up = Linear(tensors[self.prefix + up])
+        self.down = Linear(tensors[self.prefix + down])
+
+    def own_weights(self):
+        return [self.up.weight, self.down.weight]
+
+    def forward(self, ctx, h, out):
+        n = ctx.n_tokens
+        with ctx.ws.scope():
+            a = ctx.ws.alloc((n, self.inner), self.runtime.dtype)
+            if n > 64 and ops.tc_supported(h, self.up.weight, a):
+                ops.gemm_tc_act(h, self.up.weight, a, self.runtime.status, self.activation)       # in the epilogue
+            else:
+                z = ctx.ws.alloc((ctx.max_slabs, n, self.inner), torch.float32)
+                parts = self.up.slabs(ctx, h, z)
+                ops.activation(z[0], a, self.activation, n_partials=parts, partial_stride=z.stride(0))
+            ctx.to_stream(self.down, a)
+
+
 register_part("feed_forward", "gated_mlp", GatedMLP)
+register_part("feed_forward", "mlp", PlainMLP)

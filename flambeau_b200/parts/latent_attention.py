@@ -16,7 +16,7 @@ class LatentAttention(Mixer):
         [z : Rc | zr : r] = Wdkv h;  c = rmsnorm(z) * wc;  kr = rot(zr)        (one rotated key part for all heads)
         k_h = [Wuk_h c | kr];  v_h = Wuv_h c
         s_ij = scale * (qn_h . Wuk_h c_j + rot(qr_h) . kr_j)  over the keys with 0 <= i - j < window (0: all earlier)
-        out = Wo ((softmax(s) v)_heads * sigmoid(Wg h))
+        out = Wo ((softmax(s) v)_heads * sigmoid(Wg h))                       (`gate` False: no Wg, the heads as they are)
 
     Only [c | kr] is cached, once per token and not per head.  Keys and values are never formed: the query is carried
     into the latent (Wuk_h^T qn_h, a map per head) so that the attention runs as one shared key/value head of size
@@ -24,17 +24,20 @@ class LatentAttention(Mixer):
     (another map per head), which is the same arithmetic.  `shares_latent`: the mixer has no Wdkv; the layer call
     reads the cache that another call owns (LayerCall.cache_from), with its own Wuk, Wuv, queries and window.
     `keep_window`: how many keys the cache must keep (an owner whose readers look further back than itself).
+    The position part turns the rotated part of a head: it hands out its tables (`half`, `prepare`) and says which
+    dimensions form a pair (`pairing`: neighbours (2i, 2i + 1) or halves (i, i + half)).
     Rotation angles, both RMS norms, scores and softmax weights are float32 in both engine modes; the weights enter
     the product with the latents as two bfloat16 numbers each when serving.
 
-    Tensors behind the prefix: dq, dq.norm, uq, dkv, dkv.norm, uk, uv, g, o."""
+    Tensors behind the prefix: dq, dq.norm, uq, dkv, dkv.norm, uk, uv, g (with `gate`), o."""
     graph_safe = True
 
     def __init__(self, runtime=None, prefix="", *, width: int, num_heads: int, head_dim: int, rot_dim: int,
                  value_dim: int, kv_rank: int, q_rank: int, window: int, scale: float, eps: float,
                  position: PartSpec | None = None, shares_latent: bool = False, keep_window: int | None = None,
-                 init_std: float = 0.02):
+                 init_std: float = 0.02, gate: bool = True):
         super().__init__(runtime, prefix)
+        self.gate = bool(gate)
         self.width, self.H, self.d, self.r, self.e = int(width), int(num_heads), int(head_dim), int(rot_dim), int(value_dim)
         self.Rc, self.Rq, self.window = int(kv_rank), int(q_rank), int(window or 0)
         self.keep_window = self.window if keep_window is None else int(keep_window)
@@ -62,9 +65,10 @@ class LatentAttention(Mixer):
             p + "uq": TensorSpec((self.H * (self.d + self.r), self.Rq), init=init),
             p + "uk": TensorSpec((self.H * self.d, self.Rc), init=init),
             p + "uv": TensorSpec((self.H * self.e, self.Rc), init=init),
-            p + "g": TensorSpec((self.H * self.e, self.width), init=init),
             p + "o": TensorSpec((self.width, self.H * self.e), init=init),
         }
+        if self.gate:
+            specs[p + "g"] = TensorSpec((self.H * self.e, self.width), init=init)
         if not self.shares_latent:
             specs[p + "dkv"] = TensorSpec((self.hd, self.width), init=init)
             specs[p + "dkv.norm"] = TensorSpec((self.Rc,), init=norm)
@@ -72,7 +76,8 @@ class LatentAttention(Mixer):
 
     def own_bind(self, tensors):
         p = self.prefix
-        stack = [tensors[p + "dq"]] + ([] if self.shares_latent else [tensors[p + "dkv"]]) + [tensors[p + "g"]]
+        stack = [tensors[p + "dq"]] + ([] if self.shares_latent else [tensors[p + "dkv"]]) + \
+            ([tensors[p + "g"]] if self.gate else [])
         rows = sum(t.shape[0] for t in stack)
         self.kv_off = self.Rq
         self.gate_off = self.Rq + (0 if self.shares_latent else self.hd)
@@ -99,6 +104,7 @@ class LatentAttention(Mixer):
         H, d, r, e, Rc, hd = self.H, self.d, self.r, self.e, self.Rc, self.hd
         pos = self.position
         half = pos.half if pos is not None else 0
+        pairing = getattr(pos, "pairing", "neighbours")
         with ctx.ws.scope():
             slabs = ctx.ws.alloc((ctx.max_slabs, n, self.proj.out_features), torch.float32)
             parts = self.proj.slabs(ctx, h, slabs)
@@ -106,17 +112,18 @@ class LatentAttention(Mixer):
             cos, sin = pos.prepare(ctx) if half else (None, None)
             cq = ctx.ws.alloc((n, self.Rq), rt.dtype)
             ops.mla_latents(slabs[0], self.Rq, self.q_norm, cq, self.kv_off, Rc, r, self.c_norm, self.eps, cos, sin,
-                            half, cache, b.positions, b.row_seq, rt.status, n_partials=parts, partial_stride=stride)
+                            half, cache, b.positions, b.row_seq, rt.status, n_partials=parts, partial_stride=stride,
+                            pairing=pairing)
             qs = ctx.ws.alloc((ctx.max_slabs, n, H * (d + r)), torch.float32)
             q_parts = self.uq.slabs(ctx, cq, qs)
             q = ctx.ws.alloc((n, H * hd), rt.dtype)
             ops.head_linear(qs[0], d + r, self.uk_t, q, hd, n, n_partials=q_parts, partial_stride=qs.stride(0),
-                            cos=cos, sin=sin, half=half, rot=r)
+                            cos=cos, sin=sin, half=half, rot=r, pairing=pairing)
             a = ctx.ws.alloc((n, H * hd), rt.dtype)
             ops.paged_attention(ctx, q, a, cache, H, 1, hd, self.window, self.scale, vd=hd, weights_float32=True)
             og = ctx.ws.alloc((n, H * e), rt.dtype)
-            ops.head_linear(a, hd, self.uv, og, e, n, gate=slabs[0], gate_off=self.gate_off, gate_partials=parts,
-                            gate_partial_stride=stride)
+            ops.head_linear(a, hd, self.uv, og, e, n, gate=slabs[0] if self.gate else None, gate_off=self.gate_off,
+                            gate_partials=parts, gate_partial_stride=stride)
             ctx.to_stream(self.o, og)
 
 

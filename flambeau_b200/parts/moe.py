@@ -16,7 +16,12 @@ class RoutedExperts(FeedForward):
       'softmax_of_chosen' (the default): the `top` experts with the largest z + br are chosen (the lower index wins a
         tie) and their shares are the softmax over the chosen logits only;
       'softmax_of_all': scores s = softmax(z) over all experts; the `top` largest of s + br are chosen (br only moves
-        the choice); the shares are the chosen scores themselves over their sum (+ 1e-20), times `weight_scale`.
+        the choice); the shares are the chosen scores themselves over their sum (+ 1e-20), times `weight_scale`;
+      'sigmoid': scores s = sigmoid(z), every logit by itself; the `top` largest of s + br are chosen; the shares are
+        the chosen scores as they are, times `weight_scale`.
+    `share_on_input`: the share multiplies what the expert reads instead of what it gives, d = sum expert_e(share_e h)
+    (the rows are scaled as they are laid side by side in expert order; with experts that are not linear in their
+    input this is another function than the weighted sum of outputs).
     An expert is Wdown act(Wup h) with `activation` one of kernels.ops.PLAIN_ACTIVATIONS, or, with `gated`,
     Wdown (act(Wgate h) * (Wup h)) with `activation` one of kernels.ops.ACTIVATIONS; experts have no biases.
     `identity` (a count): that many more router outputs, behind the experts', stand for experts without weights
@@ -40,10 +45,13 @@ class RoutedExperts(FeedForward):
                  activation: str = "relu_squared", shared_inner: int | None = None, router_bias: bool = True,
                  init_std: float = 0.02, router_std: float = 0.5, gated: bool = False,
                  rule: str = "softmax_of_chosen", weight_scale: float = 1.0, identity: int = 0,
-                 bias_name: str = "router.b", shared: PartSpec | None = None):
+                 bias_name: str = "router.b", shared: PartSpec | None = None, share_on_input: bool = False):
         super().__init__(runtime, prefix)
         self.width, self.inner, self.E, self.K = int(width), int(inner), int(experts), int(top)
         self.identity = int(identity)
+        self.share_on_input = bool(share_on_input)
+        if self.share_on_input and self.identity:
+            raise ValueError("routed experts: shares on the experts' inputs and experts without weights do not go together")
         self.outputs = self.E + self.identity            # what the router tells apart
         if not 1 <= self.K <= self.outputs:
             raise ValueError(f"top = {self.K} of {self.outputs} experts")
@@ -152,13 +160,17 @@ class RoutedExperts(FeedForward):
             place_token = ctx.ws.alloc((rows,), torch.int32)
             pair_place = ctx.ws.alloc((pairs,), torch.int32)
             tile_expert = ctx.ws.alloc((max_tiles,), torch.int32)
+            # (shares on the inputs: the gather wants to know which pair a place stands for)
+            place_pair = ctx.ws.alloc((rows,), torch.int32) if self.share_on_input else None
             # (a choice beyond the experts that have weights gets no place: the combine hands the token's input on)
-            ops.moe_sort(chosen, E, tile, place_token, pair_place, tile_expert)
+            ops.moe_sort(chosen, E, tile, place_token, pair_place, tile_expert, place_pair)
             act = ctx.ws.alloc((rows, self.inner), rt.dtype)
+            scaled = dict(row_share=share.view(-1), row_pair=place_pair) if self.share_on_input else {}
             if self.gated:
-                ops.grouped_gated_linear(h[:n], place_token, self.up, tile_expert, tile, act, self.activation, ctx)
+                ops.grouped_gated_linear(h[:n], place_token, self.up, tile_expert, tile, act, self.activation, ctx,
+                                         **scaled)
             else:
-                ops.grouped_linear(h[:n], place_token, self.up, tile_expert, tile, act, self.activation, ctx)
+                ops.grouped_linear(h[:n], place_token, self.up, tile_expert, tile, act, self.activation, ctx, **scaled)
             y = ctx.ws.alloc((rows, D), torch.float32)
             ops.grouped_linear(act, None, self.down, tile_expert, tile, y, None, ctx)
             shared, shared_parts, shared_stride = None, 1, 0
@@ -172,8 +184,8 @@ class RoutedExperts(FeedForward):
                 shared, shared_stride = sh[0], sh.stride(0)
             elif self.shared is not None:
                 shared, shared_parts, shared_stride = self._shared_part(ctx, h, n)
-            ops.moe_combine(y, pair_place, share, shared, shared_parts, shared_stride, gate, out, n,
-                            pass_on=h[:n] if self.identity else None)
+            ops.moe_combine(y, pair_place.view(n, K), None if self.share_on_input else share, shared, shared_parts,
+                            shared_stride, gate, out, n, pass_on=h[:n] if self.identity else None)
         ctx.pending_slabs = 1
 
 

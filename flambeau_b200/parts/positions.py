@@ -19,6 +19,7 @@ class RotaryHalf(PositionEncoding):
     graph_safe = True
 
     fused_with_cache_write = True      # the attention mixer may hand the tables to its fused kernel
+    pairing = "halves"                 # which dimensions form pair i (kernels.ops.ROTARY_PAIRING)
 
     def __init__(self, runtime=None, prefix="", *, head_dim: int, theta: float, rotary_dim: int | None = None):
         super().__init__(runtime, prefix)
@@ -74,6 +75,7 @@ class RotaryNeighbours(PositionEncoding):
     graph_safe = True
 
     fused_with_cache_write = False     # the split-half kernels do not take these tables; mixers that do ask prepare()
+    pairing = "neighbours"             # which dimensions form pair i (kernels.ops.ROTARY_PAIRING)
 
     def __init__(self, runtime=None, prefix="", *, head_dim: int, theta: float, rotary_dim: int | None = None,
                  stretch: dict | None = None):

@@ -5,8 +5,8 @@ for shapes too large to be worth a file.
 Each tensor is drawn from a generator seeded with (seed, tensor name), so the
 values do not depend on the order of generation or on which other tensors
 exist.  Linear maps and embeddings are N(0, std); norm weights are
-1 + N(0, std) or ones, as their TensorSpec says (and the weights of a mean over depth N(0, std) with one added to
-the newest entry's).
+1 + N(0, std) or ones, as their TensorSpec says (the weights of a mean over depth N(0, std) with one added to
+the newest entry's; those of several residual streams c + N(0, std), and the identity + N(0, std) for their mix).
 """
 from __future__ import annotations
 
@@ -35,7 +35,11 @@ def draw(spec, seed: int, name: str, device="cpu") -> torch.Tensor:
         return torch.zeros(spec.shape, dtype=torch.int32, device=device)
     if kind == "ones":
         return torch.ones(spec.shape, dtype=torch.float32, device=device)
-    noise = torch.randn(spec.shape, generator=g, dtype=torch.float32, device=device) * float(spec.init[1])
+    noise = torch.randn(spec.shape, generator=g, dtype=torch.float32, device=device) * float(spec.init[-1])
+    if kind == "normal_around":               # ('normal_around', centre, std)
+        return float(spec.init[1]) + noise
+    if kind == "identity_plus_normal":        # a square matrix near the identity
+        return torch.eye(spec.shape[-1], dtype=torch.float32, device=device) + noise
     if kind == "normal":
         return noise
     if kind == "one_plus_normal":
