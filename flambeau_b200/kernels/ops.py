@@ -772,7 +772,7 @@ def paged_attention_mma(q, out, k_pool, v_pool, block_table, seq_q_start, seq_q_
         1 if any_short else 0,
         1 if any_long else 0, nh, nkv, hd, int(window), int(keep_first), float(scale), _slopes(score_slopes, nh), _ptr(sinks),
         1 if weights_float32 else 0, scratch.data_ptr(), scratch.numel(),
-        *prefetch_arguments(prefetch), status.data_ptr(), _stream()), "paged_attention_mma")
+        *prefetch_arguments(prefetch), status.data_ptr(), _stream()), "paged_attention_mma", (n_seqs, nkv, hd))
 
 
 def attention_kv_share(nh: int, nkv: int) -> int:

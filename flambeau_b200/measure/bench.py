@@ -32,6 +32,7 @@ A "step" is one decode step.  It prints ONE JSON line:
 size, decode and prefill tokens a second and the kernels that differ (flambeau_b200/measure/compare.py).
 `--only nodepel` likewise: the Nodepel design beside Mistral (flambeau_b200/measure/compare_nodepel.py; --sizes 1b,7b).
 `--only fegizen` likewise: the Fegizen design beside Nodepel (flambeau_b200/measure/compare_fegizen.py; --sizes 1b,7b).
+`--only tubepel` likewise: the Tubepel design beside Fegizen (flambeau_b200/measure/compare_tubepel.py; --sizes 1b,7b).
 
 The cache of the timed sequences is laid out by the cache manager exactly as a real request of that length
 leaves it (pages taken and, under the window, given back), but its keys and values are random numbers rather than
@@ -87,7 +88,7 @@ def main(argv=None) -> int:
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has (sizes unchanged)")
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--skip-points", action="store_true", help="do not measure batch 1 and 64")
-    ap.add_argument("--only", choices=["all", "headline", "mixed", "shapes", "timeline", "mma-issue", "zedivik", "nodepel", "fegizen"],
+    ap.add_argument("--only", choices=["all", "headline", "mixed", "shapes", "timeline", "mma-issue", "zedivik", "nodepel", "fegizen", "tubepel"],
                     default="all",
                     help="headline: the shape's own line only; mixed / shapes: that part only; timeline: the kernels "
                          "of one decode step at --batch as the device ran them (a table on stderr, 4 layers unless "
@@ -204,6 +205,18 @@ def main(argv=None) -> int:
             result = compare_fegizen.run(sizes, args.layers or 4, args.batch, args.prefill_tokens, min(args.steps, 64),
                                          args.warmup, pk, gen, say)
         print(json.dumps({"impl": "ours", "metric": "Fegizen beside Nodepel at equal size: decode and prefill tok/s, "
+                          "per-kernel microseconds per launch", "dtype": "bf16", "data": "synthetic", "peak": tag,
+                          "peaks": {"hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"]},
+                          "compare": result, "clocks": clocks.summary()}))
+        return 0
+    if args.only == "tubepel":
+        from flambeau_b200.measure import compare_tubepel
+        with ClockSampler(0) as clocks:
+            time.sleep(0.3)
+            sizes = [k for k in args.sizes.split(",") if k in compare_tubepel.SIZES]
+            result = compare_tubepel.run(sizes, args.layers or 4, args.batch, args.prefill_tokens, min(args.steps, 64),
+                                         args.warmup, pk, gen, say)
+        print(json.dumps({"impl": "ours", "metric": "Tubepel beside Fegizen at equal size: decode and prefill tok/s, "
                           "per-kernel microseconds per launch", "dtype": "bf16", "data": "synthetic", "peak": tag,
                           "peaks": {"hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"]},
                           "compare": result, "clocks": clocks.summary()}))
