@@ -16,7 +16,8 @@
 
 constexpr int HC_MAX_STREAMS = 8;
 
-template <typename TW, typename TO, int VEC>
+// SMAX: the most copies this instance holds in registers (2, 4 or 8), so that a row of few copies does not pay for eight.
+template <typename TW, typename TO, int VEC, int SMAX>
 __global__ void __launch_bounds__(256)
 hc_step_kernel(float* __restrict__ xs, long stream_stride, int S, const float* __restrict__ y, int n_partials,
                long partial_stride, const float* __restrict__ mix, const float* __restrict__ out_w,
@@ -41,9 +42,9 @@ hc_step_kernel(float* __restrict__ xs, long stream_stride, int S, const float* _
     const float* yr = y ? y + (size_t)r * D : nullptr;
     float ss = 0.0f;
     for (int c = tid * VEC; c < D; c += blockDim.x * VEC) {
-        float xv[HC_MAX_STREAMS][VEC], yv[VEC], u[VEC];
+        float xv[SMAX][VEC], yv[VEC], u[VEC];
 #pragma unroll
-        for (int s = 0; s < HC_MAX_STREAMS; ++s) {
+        for (int s = 0; s < SMAX; ++s) {
             if (s >= S) break;
             if constexpr (VEC == 4) {
                 const float4 v = *reinterpret_cast<const float4*>(xr + (size_t)s * stream_stride + c);
@@ -65,13 +66,13 @@ hc_step_kernel(float* __restrict__ xs, long stream_stride, int S, const float* _
             }
         }
 #pragma unroll
-        for (int t = 0; t < HC_MAX_STREAMS; ++t) {
+        for (int t = 0; t < SMAX; ++t) {
             if (t >= S) break;
             float nv[VEC];
 #pragma unroll
             for (int e = 0; e < VEC; ++e) nv[e] = c_out[t] * yv[e];
 #pragma unroll
-            for (int s = 0; s < HC_MAX_STREAMS; ++s) {
+            for (int s = 0; s < SMAX; ++s) {
                 if (s >= S) break;
                 const float m = c_mix[s * S + t];
 #pragma unroll
@@ -128,12 +129,16 @@ FB_API int fb_hc_step(float* xs, long long stream_stride, int S, const float* y,
     const int per = vec ? 4 : 1;
     int threads = ((D / per + 31) / 32) * 32;
     threads = threads < 32 ? 32 : threads > 256 ? 256 : threads;
-#define HC_LAUNCH(V)                                                                                                   \
+#define HC_LAUNCH(V, M)                                                                                                \
     FB_DISPATCH_DTYPE(w_dtype, TW, FB_DISPATCH_DTYPE(out_dtype, TO,                                                    \
-        (fb_launch((hc_step_kernel<TW, TO, V>), dim3(n_out), dim3(threads), smem, stream, xs, (long)stream_stride, S,  \
-                   y, n_partials, (long)partial_stride, mix, out_w, in_w, (const TW*)norm_w, eps, w_offset, (TO*)out,  \
-                   rows, write_back, D))))
-    if (vec) HC_LAUNCH(4); else HC_LAUNCH(1);
+        (fb_launch((hc_step_kernel<TW, TO, V, M>), dim3(n_out), dim3(threads), smem, stream, xs, (long)stream_stride,  \
+                   S, y, n_partials, (long)partial_stride, mix, out_w, in_w, (const TW*)norm_w, eps, w_offset,         \
+                   (TO*)out, rows, write_back, D))))
+    if (vec) {
+        if (S <= 2) HC_LAUNCH(4, 2); else if (S <= 4) HC_LAUNCH(4, 4); else HC_LAUNCH(4, 8);
+    } else {
+        HC_LAUNCH(1, 8);
+    }
 #undef HC_LAUNCH
     return fb_check_launch("hc_step");
 }
