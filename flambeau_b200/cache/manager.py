@@ -47,11 +47,13 @@ class LayerCacheView:
     k_pool: Optional[torch.Tensor]
     v_pool: Optional[torch.Tensor]
     block_table: Optional[torch.Tensor]       # device int32 [sequences of the step, table columns]: live pages only
-    table_base: Optional[torch.Tensor] = None # device int32 [sequences]: the logical page column 0 stands for
+    table_base: Optional[torch.Tensor] = None # device int32 [sequences]: the logical page that the first column behind
+                                              # the kept pages' stands for
     page_size: int = 16
     writable: bool = False
     group: int = -1
     state: Optional[torch.Tensor] = None      # [slots, *shape] for mixers with fixed-size state
+    table_head: int = 0                       # the first columns of a table row: the request's kept first pages
 
 
 class PageView:
@@ -193,14 +195,17 @@ class CacheManager:
                 sd = dtype if plan.state.dtype == "engine" else getattr(torch, plan.state.dtype)
                 self.state[ci] = torch.zeros((self.max_requests, *plan.state.shape), dtype=sd, device=device)
         self.books = Books([g.n_pages for g in self.groups], [g.req.release_window for g in self.groups], self.page_size,
-                           self.max_requests, self.max_pages_per_request)
+                           self.max_requests, self.max_pages_per_request,
+                           keep_first=[g.req.keep_first if g.req.release_window > 0 else 0 for g in self.groups])
         # Columns of a block-table row: the most live pages a request holds in any group.  A group with a window W
         # keeps, while a step of k new tokens runs, the pages from position length - W + 1 to length + k.
         self.table_pages = 1
         for g in self.groups:
             live = self.max_pages_per_request
+            kept = g.req.kept_pages(self.page_size)
+            live = max(live, kept)              # (the kept pages have their columns even while a request is shorter)
             if g.req.release_window > 0 and self.max_step_tokens:
-                live = min(live, -(-(g.req.release_window + self.max_step_tokens) // self.page_size) + 2)
+                live = min(live, -(-(g.req.release_window + self.max_step_tokens) // self.page_size) + 2 + kept)
             self.table_pages = max(self.table_pages, live)
         for g in self.groups:
             g.pool = PoolView(self.books, g.index)
@@ -280,9 +285,8 @@ class CacheManager:
         snap = Snapshot(length=rec.length, first_pages=[self.books.first_live_page(rec.slot, g.index)
                                                         for g in self.groups])
         for g in self.groups:
-            ids = [p for p in rec.pages[g.index] if p >= 0]
             # only pages that hold committed tokens (pages reserved ahead of the length hold nothing yet)
-            ids = ids[:max(0, -(-rec.length // self.page_size) - snap.first_pages[g.index])]
+            ids = [p for p in list(rec.pages[g.index])[:-(-rec.length // self.page_size)] if p >= 0]
             index = torch.tensor(ids, dtype=torch.long, device=self.device)
             for c in g.owners:
                 snap.k[c] = g.k[c].index_select(0, index).cpu()
@@ -332,7 +336,7 @@ class CacheManager:
         owner = plan.cache_from if plan.cache_from is not None else call
         g = self.groups[gi]
         return LayerCacheView(g.k[owner], g.v[owner], tables[gi], table_bases[gi] if table_bases else None,
-                              self.page_size, plan.cache_from is None, gi, state)
+                              self.page_size, plan.cache_from is None, gi, state, g.req.kept_pages(self.page_size))
 
     def first_live_page(self, request_id, group: int) -> int:
         """The logical page index that the request's block-table row starts at in `group`."""

@@ -36,17 +36,20 @@ def _ptr(a: np.ndarray):
 
 
 class Books:
-    """One cache's books: `n_pages[g]` pages and window `windows[g]` (0 = none) for each group g."""
+    """One cache's books: `n_pages[g]` pages, window `windows[g]` (0 = none) and `keep_first[g]` first keys that stay
+    visible under the window (their pages are never given back while a request lives) for each group g."""
 
-    def __init__(self, n_pages: list, windows: list, page_size: int, max_requests: int, max_pages_per_request: int):
+    def __init__(self, n_pages: list, windows: list, page_size: int, max_requests: int, max_pages_per_request: int,
+                 keep_first: list | None = None):
         if any(n <= 0 for n in n_pages):
             raise ValueError("a page pool needs at least one page")
         self._lib = lib()
         self.n_groups = len(n_pages)
         self._scratch = np.zeros(max(self.n_groups, 1), dtype=np.int32)
         self._h = self._lib.fbh_cache_new(self.n_groups, _ptr(_ints(n_pages if n_pages else [0])),
-                                          _ptr(_ints(windows if windows else [0])), int(page_size), int(max_requests),
-                                          int(max_pages_per_request))
+                                          _ptr(_ints(windows if windows else [0])),
+                                          _ptr(_ints(keep_first if keep_first else [0] * max(self.n_groups, 1))),
+                                          int(page_size), int(max_requests), int(max_pages_per_request))
         if not self._h:
             raise PageError(self._message())
 
@@ -79,7 +82,8 @@ class Books:
         return self._ok(self._lib.fbh_admit(self._h))
 
     def admit_at(self, length: int, first_pages) -> int:
-        """A slot for a request of `length` tokens whose group g holds its pages from first_pages[g] on."""
+        """A slot for a request of `length` tokens whose group g holds its kept first pages and its pages from
+        first_pages[g] on."""
         fp = _ints(first_pages if len(first_pages) else [0])
         return self._ok(self._lib.fbh_admit_at(self._h, int(length), _ptr(fp)))
 

@@ -41,8 +41,11 @@ struct AttnArgs {
     const __nv_bfloat16* k_pool; const __nv_bfloat16* v_pool;
     int page_size, n_pages;
     const int* block_table; int table_stride;
-    const int* table_base;             // per sequence: the logical page that column 0 of its table row stands for
-                                       // (nullptr: page 0); released leading pages are not in the table
+    const int* table_base;             // per sequence: the logical page that the first column behind the kept pages'
+                                       // of its table row stands for (nullptr: page 0); released pages are not in
+                                       // the table
+    int table_head;                    // the first columns of every table row hold the request's first pages, which
+                                       // it keeps (fb_table_column); 0 as a rule
     const int* seq_q_start; const int* seq_q_len; const int* seq_pos_start;
     const int* multi_seqs; int n_multi;   // the sequences that bring more than one token, in step order: the grid of
                                           // the arrangements for portions covers only these (nullptr: all n_seqs)
@@ -78,7 +81,7 @@ __device__ __forceinline__ float sink_term(const AttnArgs& a, int head, float m)
 // The page id of logical page `logical` of a sequence whose table row `table` starts at logical page `base_page`
 // (-1 where the row has no such column).
 __device__ __forceinline__ int table_page(const AttnArgs& a, const int* table, int base_page, int logical) {
-    const int e = logical - base_page;
+    const int e = fb_table_column(logical, base_page, a.table_head);
     return (e >= 0 && e < a.table_stride) ? table[e] : -1;
 }
 __device__ __forceinline__ int table_base_of(const AttnArgs& a, int seq) { return a.table_base ? a.table_base[seq] : 0; }

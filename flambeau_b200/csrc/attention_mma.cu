@@ -457,7 +457,7 @@ FB_API void fb_set_attention_tc(int on) { g_attention_tc = on ? 1 : 0; }
 // the product that follows (a hint; null base: none).
 FB_API int fb_paged_attention_mma(const void* q, long long q_stride, void* out, long long out_stride,
                                   const void* k_pool, const void* v_pool, int page_size, int n_pages,
-                                  const int* block_table, int table_stride, const int* table_base,
+                                  const int* block_table, int table_stride, const int* table_base, int table_head,
                                   const int* seq_q_start, const int* seq_q_len, const int* seq_pos_start,
                                   const int* multi_seqs, int n_multi, int n_seqs, int max_q_len, int max_kv_len, int any_short, int any_long, int nh, int nkv, int hd,
                                   int window, int keep_first, float scale, const float* score_slopes, const float* sinks,
@@ -482,6 +482,7 @@ FB_API int fb_paged_attention_mma(const void* q, long long q_stride, void* out, 
     a.k_pool = (const __nv_bfloat16*)k_pool; a.v_pool = (const __nv_bfloat16*)v_pool;
     a.page_size = page_size; a.n_pages = n_pages;
     a.block_table = block_table; a.table_stride = table_stride; a.table_base = table_base;
+    a.table_head = table_head > 0 ? table_head : 0;
     a.seq_q_start = seq_q_start; a.seq_q_len = seq_q_len; a.seq_pos_start = seq_pos_start;
     a.multi_seqs = multi_seqs; a.n_multi = n_multi;
     a.nh = nh; a.nkv = nkv; a.hd = hd; a.window = window;

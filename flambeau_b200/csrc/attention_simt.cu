@@ -23,7 +23,7 @@ __global__ void __launch_bounds__(128)
 paged_attention_simt_kernel(const T* __restrict__ q, long q_stride, T* __restrict__ out, long out_stride,
                             const T* __restrict__ k_pool, const T* __restrict__ v_pool, int page_size,
                             int n_pages, const int* __restrict__ block_table, int table_stride,
-                            const int* __restrict__ table_base,
+                            const int* __restrict__ table_base, int table_head,
                             const int* __restrict__ positions, const int* __restrict__ row_seq, int n, int nh,
                             int nkv, int hd, int vd, int window, int keep_first, float scale,
                             const float* __restrict__ score_slopes, const float* __restrict__ sinks, int* status) {
@@ -65,7 +65,7 @@ paged_attention_simt_kernel(const T* __restrict__ q, long q_stride, T* __restric
         float s = -INFINITY;
         int my_page = -1;
         if (valid) {
-            const int entry = t / page_size - base_page;
+            const int entry = fb_table_column(t / page_size, base_page, table_head);
             my_page = (entry >= 0 && entry < table_stride) ? table[entry] : -1;
             if (my_page < 0 || my_page >= n_pages) {
                 atomicOr(status, FB_STATUS_BAD_PAGE);
@@ -121,7 +121,7 @@ paged_attention_simt_kernel(const T* __restrict__ q, long q_stride, T* __restric
 template <typename T, int NDR>
 static int launch_attention_simt(const void* q, long q_stride, void* out, long out_stride, const void* k_pool,
                                  const void* v_pool, int page_size, int n_pages, const int* block_table,
-                                 int table_stride, const int* table_base, const int* positions, const int* row_seq,
+                                 int table_stride, const int* table_base, int table_head, const int* positions, const int* row_seq,
                                  int n, int nh,
                                  int nkv, int hd, int vd, int window, int keep_first, float scale, const float* score_slopes,
                                  const float* sinks, int* status, cudaStream_t stream) {
@@ -129,14 +129,14 @@ static int launch_attention_simt(const void* q, long q_stride, void* out, long o
     const unsigned blocks = (unsigned)((items + 3) / 4);
     fb_launch((paged_attention_simt_kernel<T, NDR>), blocks, 128, 4 * hd * sizeof(float), stream, 
         (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_pool, (const T*)v_pool, page_size, n_pages,
-        block_table, table_stride, table_base, positions, row_seq, n, nh, nkv, hd, vd, window, keep_first, scale, score_slopes, sinks,
+        block_table, table_stride, table_base, table_head, positions, row_seq, n, nh, nkv, hd, vd, window, keep_first, scale, score_slopes, sinks,
         status);
     return fb_check_launch("paged_attention_simt");
 }
 
 FB_API int fb_paged_attention_simt(const void* q, long long q_stride, void* out, long long out_stride, int dtype,
                                    const void* k_pool, const void* v_pool, int page_size, int n_pages,
-                                   const int* block_table, int table_stride, const int* table_base,
+                                   const int* block_table, int table_stride, const int* table_base, int table_head,
                                    const int* positions, const int* row_seq, int n, int nh, int nkv, int hd,
                                    int vd, int window, int keep_first, float scale, const float* score_slopes, const float* sinks,
                                    int* status, cudaStream_t stream) {
@@ -148,7 +148,7 @@ FB_API int fb_paged_attention_simt(const void* q, long long q_stride, void* out,
     if (n == 0) return 0;
 #define FB_ATTN_CASE(NDR)                                                                                      \
     FB_DISPATCH_DTYPE(dtype, T, return (launch_attention_simt<T, NDR>(q, (long)q_stride, out, (long)out_stride,     \
-        k_pool, v_pool, page_size, n_pages, block_table, table_stride, table_base, positions, row_seq, n, nh, \
+        k_pool, v_pool, page_size, n_pages, block_table, table_stride, table_base, table_head, positions, row_seq, n, nh, \
         nkv, hd, vd, window, keep_first, scale, score_slopes, sinks, status, stream)))
     if (vd <= 32) { FB_ATTN_CASE(1); }
     else if (vd <= 64) { FB_ATTN_CASE(2); }

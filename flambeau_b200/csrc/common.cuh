@@ -131,6 +131,15 @@ __device__ __forceinline__ void fb_prefetch_issue(const FbPrefetch& pf, long wor
         asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(pf.base + r * pf.row_stride), "r"(pf.bytes) : "memory");
 }
 
+// ---- block tables -------------------------------------------------------------
+// The column of a request's table row that holds logical page `logical`.  The row's first `head` columns are the
+// request's first `head` logical pages, which it keeps while it lives (the first keys under a window that keeps
+// them visible; 0 as a rule); the columns behind them are its live pages from logical page `base` on.  Negative
+// where the row has no column for the page (given back).
+__host__ __device__ __forceinline__ int fb_table_column(int logical, int base, int head) {
+    return logical < head ? logical : (logical >= base ? logical - base + head : -1);
+}
+
 // ---- typed access -----------------------------------------------------------
 __device__ __forceinline__ float fb_to_float(float v) { return v; }
 __device__ __forceinline__ float fb_to_float(__nv_bfloat16 v) { return __bfloat162float(v); }

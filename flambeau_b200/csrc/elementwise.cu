@@ -522,8 +522,9 @@ FB_API int fb_rope_table(const int* positions, const double* inv_freq, float* co
 // Rotary (split-half pairs (i, i+half)) on q in place and on k on its way into
 // the cache; v is copied into the cache.  One block per token.
 // Cache layout: [page][kv head][slot in page][head_dim]; the physical page of
-// logical position p of sequence s is block_table[s*table_stride + p/page_size - table_base[s]]: a table row
-// starts at the sequence's first live page (table_base == nullptr: at page 0).
+// logical position p of sequence s is block_table[s*table_stride + fb_table_column(p/page_size, table_base[s],
+// table_head)]: a table row holds the sequence's kept first pages (table_head of them, 0 as a rule), then its pages
+// from its first live page on (table_base == nullptr: from page 0).
 // crates/kernels-hip/src/kernels/rope_neox_partial_f16.cu:39-52 (rotation),
 // kv_append_f16_paged_prefill.cu (row placement).
 // ---------------------------------------------------------------------------
@@ -550,7 +551,7 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ q_in, long q_in_stri
                                      const float* __restrict__ sin_t, int half,
                                      const int* __restrict__ positions, const int* __restrict__ row_seq,
                                      const int* __restrict__ block_table, int table_stride,
-                                     const int* __restrict__ table_base,
+                                     const int* __restrict__ table_base, int table_head,
                                      T* __restrict__ k_pool, T* __restrict__ v_pool, int page_size, int n_pages,
                                      int nh, int nkv, int hd, int write_kv, int* status) {
     fb_pdl_launch_dependents();
@@ -581,7 +582,7 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ q_in, long q_in_stri
     const int h = hy - nh;
     const int pos = positions[t];
     const int seq = row_seq[t];
-    const int entry = pos / page_size - (table_base ? table_base[seq] : 0);
+    const int entry = fb_table_column(pos / page_size, table_base ? table_base[seq] : 0, table_head);
     const int page = (entry >= 0 && entry < table_stride) ? block_table[(size_t)seq * table_stride + entry] : -1;
     if (page < 0 || page >= n_pages) {
         if (threadIdx.x == 0) atomicOr(status, FB_STATUS_BAD_PAGE);
@@ -633,8 +634,9 @@ rope_kv_write_vec_kernel(const TI* __restrict__ q_in, long q_in_stride, int n_pa
                          const TI* __restrict__ v, long v_stride, const float* __restrict__ cos_t,
                          const float* __restrict__ sin_t, int half, const int* __restrict__ positions,
                          const int* __restrict__ row_seq, const int* __restrict__ block_table, int table_stride,
-                         const int* __restrict__ table_base, T* __restrict__ k_pool, T* __restrict__ v_pool,
-                         int page_size, int n_pages, int n, int nh, int nkv, int hd, int write_kv, int* status) {
+                         const int* __restrict__ table_base, int table_head, T* __restrict__ k_pool,
+                         T* __restrict__ v_pool, int page_size, int n_pages, int n, int nh, int nkv, int hd, int write_kv,
+                         int* status) {
     fb_pdl_launch_dependents();
     fb_pdl_wait();
     const int t0 = blockIdx.x * TOK;
@@ -661,7 +663,7 @@ rope_kv_write_vec_kernel(const TI* __restrict__ q_in, long q_in_stride, int n_pa
 #pragma unroll
         for (int i = 0; i < TOK; ++i) {
             const int seq = row_seq[tok[i]];
-            const int entry = pos[i] / page_size - (table_base ? table_base[seq] : 0);
+            const int entry = fb_table_column(pos[i] / page_size, table_base ? table_base[seq] : 0, table_head);
             page[i] = (entry >= 0 && entry < table_stride) ? block_table[(size_t)seq * table_stride + entry] : -1;
         }
 #pragma unroll
@@ -736,8 +738,8 @@ FB_API int fb_rope_kv_write(const void* q_in, long long q_in_stride, int n_parti
                             const void* k, long long k_stride, const void* v, long long v_stride, int in_dtype,
                             int out_dtype, const float* cos_t, const float* sin_t, int half,
                             const int* positions, const int* row_seq, const int* block_table,
-                            int table_stride, const int* table_base, void* k_pool, void* v_pool, int page_size,
-                            int n_pages, int n,
+                            int table_stride, const int* table_base, int table_head, void* k_pool, void* v_pool,
+                            int page_size, int n_pages, int n,
                             int nh, int nkv, int hd, int write_kv, int* status, cudaStream_t stream) {
     FB_REQUIRE(n >= 0 && nh > 0 && nkv >= 0 && hd > 0, "rope_kv_write: bad sizes");
     FB_REQUIRE(half >= 0 && 2 * half <= hd, "rope_kv_write: rotary width %d exceeds head size %d", 2 * half, hd);
@@ -762,7 +764,7 @@ FB_API int fb_rope_kv_write(const void* q_in, long long q_in_stride, int n_parti
             (fb_launch((rope_kv_write_vec_kernel<TI, T, TOK_>), dim3((n + TOK_ - 1) / TOK_, (items + 255) / 256), 256, \
                 0, stream, (const TI*)q_in, (long)q_in_stride, n_partials, (long)partial_stride, (T*)q_out,   \
                 (long)q_out_stride, (const TI*)k, (long)k_stride, (const TI*)v, (long)v_stride, cos_t, sin_t, \
-                half, positions, row_seq, block_table, table_stride, table_base, (T*)k_pool, (T*)v_pool,      \
+                half, positions, row_seq, block_table, table_stride, table_base, table_head, (T*)k_pool, (T*)v_pool, \
                 page_size, n_pages, n, nh, nkv, hd, write_kv, status))))
         if (per == 2) FB_ROPE_VEC(2); else FB_ROPE_VEC(1);
 #undef FB_ROPE_VEC
@@ -771,7 +773,7 @@ FB_API int fb_rope_kv_write(const void* q_in, long long q_in_stride, int n_parti
     FB_DISPATCH_DTYPE(in_dtype, TI, FB_DISPATCH_DTYPE(out_dtype, T,
         (fb_launch((rope_kv_write_kernel<TI, T>), dim3(n, nh + (write_kv ? nkv : 0)), hd >= 128 ? 64 : 32, 0, stream, (const TI*)q_in, q_in_stride, n_partials, (long)partial_stride, (T*)q_out, q_out_stride,
             (const TI*)k, k_stride, (const TI*)v, v_stride, cos_t, sin_t, half, positions, row_seq, block_table,
-            table_stride, table_base, (T*)k_pool, (T*)v_pool, page_size, n_pages, nh, nkv, hd, write_kv, status))));
+            table_stride, table_base, table_head, (T*)k_pool, (T*)v_pool, page_size, n_pages, nh, nkv, hd, write_kv, status))));
     return fb_check_launch("rope_kv_write");
 }
 

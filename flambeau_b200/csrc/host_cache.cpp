@@ -64,9 +64,15 @@ struct Pool {
 };
 
 struct PageList {
-    int base = 0;                   // logical pages below this index have been given back
-    std::vector<int> ids;           // the live pages: ids[i] is logical page base + i
-    int end() const { return base + (int)ids.size(); }    // logical pages [0, end()) have been taken so far
+    int keep = 0;                   // the request's first `keep` logical pages are never given back while it lives
+    int base = 0;                   // logical pages in [keep, base) have been given back (base >= keep)
+    std::vector<int> head;          // the kept pages: head[i] is logical page i (at most `keep` of them)
+    std::vector<int> ids;           // the live pages behind them: ids[i] is logical page base + i
+    explicit PageList(int keep_pages = 0) : keep(keep_pages), base(keep_pages) {}
+    // logical pages [0, end()) have been taken so far
+    int end() const { return (int)head.size() < keep ? (int)head.size() : base + (int)ids.size(); }
+    void push(int page) { ((int)head.size() < keep ? head : ids).push_back(page); }
+    int live() const { return (int)(head.size() + ids.size()); }
 };
 
 struct Record {
@@ -80,9 +86,14 @@ struct Cache {
     int page_size = 16, max_requests = 0, max_pages_per_request = 0;
     std::vector<Pool> pools;
     std::vector<int> windows;
+    std::vector<int> keep_pages;    // per group: pages that hold the first keys a window keeps visible (0 without)
     std::vector<Record> records;    // by slot
     std::vector<int> free_slots;    // a stack; the lowest slot on top at the start
     int n_groups() const { return (int)pools.size(); }
+    void fresh_lists(Record& r) const {
+        r.pages.clear();
+        for (int g = 0; g < n_groups(); ++g) r.pages.emplace_back(keep_pages[(size_t)g]);
+    }
 };
 
 Cache* as_cache(void* h) { return static_cast<Cache*>(h); }
@@ -97,9 +108,10 @@ int check_slot(const Cache& c, int slot) {
 
 FBH_API const char* fbh_last_error() { return g_error; }
 
-// n_pages[g], windows[g] (0 = all earlier keys stay live) per group.
-FBH_API void* fbh_cache_new(int n_groups, const int* n_pages, const int* windows, int page_size, int max_requests,
-                            int max_pages_per_request) {
+// n_pages[g], windows[g] (0 = all earlier keys stay live) and keep_first[g] (under a window: the first keys of a
+// request that stay visible, so the pages that hold them are kept; nullptr: none) per group.
+FBH_API void* fbh_cache_new(int n_groups, const int* n_pages, const int* windows, const int* keep_first, int page_size,
+                            int max_requests, int max_pages_per_request) {
     if (n_groups < 0 || page_size <= 0 || max_requests <= 0 || max_pages_per_request <= 0) {
         fail(ERR_STATE, "cache: bad geometry");
         return nullptr;
@@ -116,6 +128,8 @@ FBH_API void* fbh_cache_new(int n_groups, const int* n_pages, const int* windows
         }
         c->pools.emplace_back(n_pages[g]);
         c->windows.push_back(windows[g]);
+        const int keep = (keep_first && windows[g] > 0 && keep_first[g] > 0) ? keep_first[g] : 0;
+        c->keep_pages.push_back((keep + page_size - 1) / page_size);
     }
     c->records.resize((size_t)max_requests);
     for (int s = max_requests - 1; s >= 0; --s) c->free_slots.push_back(s);
@@ -135,13 +149,14 @@ FBH_API int fbh_admit(void* h) {
     Record& r = c.records[(size_t)slot];
     r.live = true;
     r.length = r.reserved_to = 0;
-    r.pages.assign((size_t)c.n_groups(), PageList());
+    c.fresh_lists(r);
     return slot;
 }
 
 // A request that comes back from a snapshot: `length` tokens whose keys are to be put back, the pages below
-// first_pages[g] of each group already given back when the snapshot was taken.  Takes a slot and the pages for
-// logical pages [first_pages[g], ceil(length / page_size)) of every group, or nothing at all; returns the slot.
+// first_pages[g] of each group (but for the group's kept first pages) already given back when the snapshot was
+// taken.  Takes a slot and the pages for the kept pages and for logical pages [first_pages[g], ceil(length /
+// page_size)) of every group, or nothing at all; returns the slot.
 FBH_API int fbh_admit_at(void* h, int length, const int* first_pages) {
     Cache& c = *as_cache(h);
     if (c.free_slots.empty()) return fail(ERR_STATE, "all %d request slots are taken", c.max_requests);
@@ -150,9 +165,10 @@ FBH_API int fbh_admit_at(void* h, int length, const int* first_pages) {
         return fail(ERR_LIMIT, "a request of %d tokens; the cache holds at most %d per request", length, limit);
     const int pages_to = (length + c.page_size - 1) / c.page_size;
     for (int g = 0; g < c.n_groups(); ++g) {
-        if (first_pages[g] < 0 || first_pages[g] > pages_to)
+        const int keep = c.keep_pages[(size_t)g];
+        if (first_pages[g] < keep || first_pages[g] > (pages_to > keep ? pages_to : keep))
             return fail(ERR_STATE, "group %d: first live page %d of a request of %d pages", g, first_pages[g], pages_to);
-        const int want = pages_to - first_pages[g];
+        const int want = (pages_to < keep ? pages_to : keep) + (pages_to > first_pages[g] ? pages_to - first_pages[g] : 0);
         if (want > c.pools[(size_t)g].n_free())
             return fail(ERR_PAGES, "%d cache pages wanted, %d of %d free", want, c.pools[(size_t)g].n_free(),
                         c.pools[(size_t)g].n_pages);
@@ -162,9 +178,10 @@ FBH_API int fbh_admit_at(void* h, int length, const int* first_pages) {
     Record& r = c.records[(size_t)slot];
     r.live = true;
     r.length = r.reserved_to = length;
-    r.pages.assign((size_t)c.n_groups(), PageList());
+    c.fresh_lists(r);
     for (int g = 0; g < c.n_groups(); ++g) {
         PageList& pl = r.pages[(size_t)g];
+        while ((int)pl.head.size() < pl.keep && (int)pl.head.size() < pages_to) pl.head.push_back(c.pools[(size_t)g].take());
         pl.base = first_pages[g];
         while (pl.end() < pages_to) pl.ids.push_back(c.pools[(size_t)g].take());
     }
@@ -177,9 +194,11 @@ FBH_API int fbh_release(void* h, int slot) {
     Record& r = c.records[(size_t)slot];
     for (int g = 0; g < c.n_groups(); ++g) {
         PageList& pl = r.pages[(size_t)g];
+        for (int id : pl.head)
+            if (int rc = c.pools[(size_t)g].give_back(id)) return rc;
         for (int id : pl.ids)
             if (int rc = c.pools[(size_t)g].give_back(id)) return rc;
-        pl = PageList();
+        pl = PageList(pl.keep);
     }
     r.live = false;
     c.free_slots.push_back(slot);
@@ -255,7 +274,7 @@ FBH_API int fbh_reserve_all(void* h, int n, const int* slots, const int* n_new, 
         const int pages_to = (end + c.page_size - 1) / c.page_size;
         for (int g = 0; g < G; ++g) {
             PageList& pl = r.pages[(size_t)g];
-            while (pl.end() < pages_to) pl.ids.push_back(c.pools[(size_t)g].take());
+            while (pl.end() < pages_to) pl.push(c.pools[(size_t)g].take());
         }
         if (end > r.reserved_to) r.reserved_to = end;
     }
@@ -277,7 +296,8 @@ FBH_API int fbh_commit(void* h, int n, const int* slots, const int* n_new) {
             if (w <= 0) continue;
             const int first_live = r.length - w + 1;          // lowest position a future query can see
             PageList& pl = r.pages[(size_t)g];
-            int dead = (first_live > 0 ? first_live : 0) / c.page_size;       // logical pages [0, dead) are dead
+            // logical pages [0, dead) are dead, but for the kept ones
+            int dead = (first_live > 0 ? first_live : 0) / c.page_size;
             if (dead > pl.end()) dead = pl.end();
             const int n_dead = dead - pl.base;
             if (n_dead > 0) {
@@ -298,11 +318,13 @@ FBH_API int fbh_pages(void* h, int slot, int group, int* out, int cap) {
     if (int rc = check_slot(c, slot)) return rc;
     const PageList& pl = c.records[(size_t)slot].pages[(size_t)group];
     const int n = pl.end();
-    for (int i = 0; out && i < n && i < cap; ++i) out[i] = i < pl.base ? -1 : pl.ids[(size_t)(i - pl.base)];
+    for (int i = 0; out && i < n && i < cap; ++i)
+        out[i] = i < (int)pl.head.size() ? pl.head[(size_t)i] : i < pl.base ? -1 : pl.ids[(size_t)(i - pl.base)];
     return n;
 }
 
-// The logical page index of the request's first live page in a group (what its table row starts at).
+// The logical page index of the request's first live page behind its kept pages in a group (what the columns of its
+// table row behind the kept pages' start at).
 FBH_API int fbh_first_live_page(void* h, int slot, int group) {
     Cache& c = *as_cache(h);
     if (int rc = check_slot(c, slot)) return rc;
@@ -318,7 +340,9 @@ FBH_API int fbh_check_invariants(void* h) {
         int n_seen = 0;
         for (const Record& r : c.records) {
             if (!r.live) continue;
-            for (int p : r.pages[(size_t)g].ids) {
+            std::vector<int> held_by(r.pages[(size_t)g].head);
+            held_by.insert(held_by.end(), r.pages[(size_t)g].ids.begin(), r.pages[(size_t)g].ids.end());
+            for (int p : held_by) {
                 if (p < 0 || p >= pool.n_pages) return fail(ERR_STATE, "group %d: page %d is outside the pool", g, p);
                 if (seen[(size_t)p]) return fail(ERR_STATE, "group %d: page %d is held twice", g, p);
                 if (!pool.held[(size_t)p]) return fail(ERR_STATE, "group %d: page %d is in a table but free in the pool", g, p);
@@ -342,9 +366,10 @@ FBH_API int fbh_check_invariants(void* h) {
 // wanted places among them (wants, concatenated, n_want[i] each).  Pages for the new tokens must be reserved.
 //   rows   [4][max_tokens]: token id, position, sequence of the row, rows whose logits are wanted
 //   seqs   [5 + groups][max_seqs]: first row, rows, first position, slot, then for each group the logical page
-//          index that column 0 of the sequence's table row stands for (its first live page), then the list of the
-//          sequences that bring more than one token (info[4] of them)
-//   tables [groups][max_seqs][max_pages]: the ids of the live pages, from the first live page on, -1 behind them
+//          index that the first column behind the kept pages' of the sequence's table row stands for (its first
+//          live page), then the list of the sequences that bring more than one token (info[4] of them)
+//   tables [groups][max_seqs][max_pages]: the group's kept first pages (as many columns as the group keeps, -1 where
+//          the request has not reached them), then the ids of the live pages from the first live page on, -1 behind
 //   fill   [groups][max_seqs]: how many entries of each table row were valid after the last call (kept by the caller)
 //   info   [5]: rows, wanted rows, longest entry, longest context, sequences with more than one token
 FBH_API int fbh_build_step(void* h, int n_entries, const int* slots, const int* q_len, const int* tokens,
@@ -397,11 +422,12 @@ FBH_API int fbh_build_step(void* h, int n_entries, const int* slots, const int* 
         for (int g = 0; g < c.n_groups(); ++g) {
             const PageList& pl = r.pages[(size_t)g];
             const std::vector<int>& ids = pl.ids;
-            const int have = (int)ids.size();
+            const int have = pl.keep + (int)ids.size();
             if (have > max_pages) return fail(ERR_BATCH, "entry %d holds %d live pages; tables have %d columns", i, have, max_pages);
             seqs[(size_t)(4 + g) * max_seqs + i] = pl.base;
             int* trow = tables + ((size_t)g * max_seqs + (size_t)i) * max_pages;
-            memcpy(trow, ids.data(), sizeof(int) * (size_t)have);
+            for (int p = 0; p < pl.keep; ++p) trow[p] = p < (int)pl.head.size() ? pl.head[(size_t)p] : -1;
+            memcpy(trow + pl.keep, ids.data(), sizeof(int) * ids.size());
             int& f = fill[(size_t)g * max_seqs + i];
             for (int p = have; p < f; ++p) trow[p] = -1;       // what an earlier step's request left in this row
             f = have;

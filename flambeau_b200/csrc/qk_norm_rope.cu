@@ -24,8 +24,9 @@ qk_norm_rope_kv_write_kernel(const float* __restrict__ proj, long proj_stride, i
                              float weight_offset, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                              int half, T* __restrict__ q_out, long q_out_stride, const int* __restrict__ positions,
                              const int* __restrict__ row_seq, const int* __restrict__ block_table, int table_stride,
-                             const int* __restrict__ table_base, T* __restrict__ k_pool, T* __restrict__ v_pool,
-                             int page_size, int n_pages, int nh, int nkv, int hd, int vd, int write_kv, int* status) {
+                             const int* __restrict__ table_base, int table_head, T* __restrict__ k_pool,
+                             T* __restrict__ v_pool, int page_size, int n_pages, int nh, int nkv, int hd, int vd,
+                             int write_kv, int* status) {
     fb_pdl_launch_dependents();
     fb_pdl_wait();
     extern __shared__ float sh[];                      // [qw + kw] the row's q and k; then one factor per head
@@ -64,7 +65,7 @@ qk_norm_rope_kv_write_kernel(const float* __restrict__ proj, long proj_stride, i
     T* v_dst = nullptr;
     if (write_kv) {
         const int p = positions[row], seq = row_seq[row];
-        const int entry = p / page_size - (table_base ? table_base[seq] : 0);
+        const int entry = fb_table_column(p / page_size, table_base ? table_base[seq] : 0, table_head);
         const int page = (entry >= 0 && entry < table_stride) ? block_table[(size_t)seq * table_stride + entry] : -1;
         if (page < 0 || page >= n_pages) {
             if (tid == 0) atomicOr(status, FB_STATUS_BAD_PAGE);
@@ -117,8 +118,8 @@ FB_API int fb_qk_norm_rope_kv_write(const float* proj, long long proj_stride, in
                                     const void* q_weight, const void* k_weight, int w_dtype, int scope, float eps,
                                     float weight_offset, const float* cos_t, const float* sin_t, int half, void* q_out,
                                     long long q_out_stride, int out_dtype, const int* positions, const int* row_seq,
-                                    const int* block_table, int table_stride, const int* table_base, void* k_pool,
-                                    void* v_pool, int page_size, int n_pages, int n, int nh, int nkv, int hd, int vd,
+                                    const int* block_table, int table_stride, const int* table_base, int table_head,
+                                    void* k_pool, void* v_pool, int page_size, int n_pages, int n, int nh, int nkv, int hd, int vd,
                                     int write_kv, int* status, cudaStream_t stream) {
     FB_REQUIRE(n >= 0 && nh > 0 && nkv > 0 && hd > 0 && vd > 0, "qk_norm_rope_kv_write: bad sizes");
     FB_REQUIRE(scope >= FB_QK_NORM_NONE && scope <= FB_QK_NORM_PROJECTION, "qk_norm_rope_kv_write: unknown reach %d", scope);
@@ -138,7 +139,7 @@ FB_API int fb_qk_norm_rope_kv_write(const float* proj, long long proj_stride, in
         const int cols = (nh + 2 * nkv) * (hd > vd ? hd : vd);
         fb_launch(kernel, dim3(n), dim3(n > 128 ? 256 : cols >= 4096 ? 1024 : cols >= 1024 ? 512 : 256), smem, stream, proj, (long)proj_stride, n_partials, (long)partial_stride,
                   (const TW*)q_weight, (const TW*)k_weight, scope, eps, weight_offset, cos_t, sin_t, half, (T*)q_out,
-                  (long)q_out_stride, positions, row_seq, block_table, table_stride, table_base, (T*)k_pool,
+                  (long)q_out_stride, positions, row_seq, block_table, table_stride, table_base, table_head, (T*)k_pool,
                   (T*)v_pool, page_size, n_pages, nh, nkv, hd, vd, write_kv, status);
     }));
     return fb_check_launch("qk_norm_rope_kv_write");

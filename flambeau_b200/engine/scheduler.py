@@ -173,10 +173,11 @@ class Scheduler:
     def _pages_for(self, tokens: int, group: int) -> int:
         """Pages that `tokens` tokens of one request hold in a group at most (a window keeps the last W tokens,
         plus the portion that is being written and the page the window starts in)."""
-        window = self.cache.groups[group].req.release_window
+        req = self.cache.groups[group].req
+        window = req.release_window
         page = self.cache.page_size
         if window:
-            tokens = min(tokens, window + self.prefill_chunk + page)
+            tokens = min(tokens, window + self.prefill_chunk + page + req.kept_pages(page) * page)
         return -(-tokens // page)
 
     def _plan_once(self, plan: PlannedStep) -> None:

@@ -31,7 +31,7 @@ _SIGNATURES = {
     "fb_concat_cast": (I, [P, P, P, I, I, I, STREAM]),
     "fb_add_rmsnorm": (I, [P, P, I, I, L, P, I, P, I, P, I, I, F, F, STREAM]),
     "fb_rope_table": (I, [P, P, P, P, I, I, F, STREAM]),
-    "fb_rope_kv_write": (I, [P, L, I, L, P, L, P, L, P, L, I, I, P, P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, P, STREAM]),
+    "fb_rope_kv_write": (I, [P, L, I, L, P, L, P, L, P, L, I, I, P, P, I, P, P, P, I, P, I, P, P, I, I, I, I, I, I, I, P, STREAM]),
     "fb_gate_mul": (I, [P, L, I, I, L, P, I, I, I, I, STREAM]),
     "fb_activation": (I, [P, L, I, I, L, P, I, I, I, I, STREAM]),
     "fb_add_row": (I, [P, P, I, I, I, STREAM]),
@@ -51,10 +51,10 @@ _SIGNATURES = {
     "fb_gemm_tc_act": (I, [P, L, P, L, P, I, L, I, I, I, I, P, STREAM]),
     "fb_gemm_tc_gated": (I, [P, L, P, L, P, I, L, I, I, I, I, P, L, P, I, P, STREAM]),
     # attention_simt.cu
-    "fb_paged_attention_simt": (I, [P, L, P, L, I, P, P, I, I, P, I, P, P, P, I, I, I, I, I, I, I, F, P, P, P, STREAM]),
+    "fb_paged_attention_simt": (I, [P, L, P, L, I, P, P, I, I, P, I, P, I, P, P, I, I, I, I, I, I, I, F, P, P, P, STREAM]),
     # qk_norm_rope.cu
-    "fb_qk_norm_rope_kv_write": (I, [P, L, I, L, P, P, I, I, F, F, P, P, I, P, L, I, P, P, P, I, P, P, P, I, I, I, I, I,
-                                     I, I, I, P, STREAM]),
+    "fb_qk_norm_rope_kv_write": (I, [P, L, I, L, P, P, I, I, F, F, P, P, I, P, L, I, P, P, P, I, P, I, P, P, I, I, I, I,
+                                     I, I, I, I, P, STREAM]),
     # gated_delta.cu
     "fb_gdr_prepare": (I, [P, L, I, L, P, I, P, P, I, P, L, L, P, P, P, P, I, P, P, P, I, I, I, I, I, F, F, STREAM]),
     "fb_gdr_recurrent": (I, [P, P, P, P, L, P, P, P, I, P, I, I, I, I, STREAM]),
@@ -88,15 +88,15 @@ _SIGNATURES = {
     "fb_diff_attention_mma": (I, [P, L, P, L, P, P, P, I, I, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, F, F, F, F, I,
                                   P, L, P, STREAM]),
     # attention_mma.cu
-    "fb_paged_attention_mma": (I, [P, L, P, L, P, P, I, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, P, P, I, P,
-                                   L, P, L, L, I, P, STREAM]),
+    "fb_paged_attention_mma": (I, [P, L, P, L, P, P, I, I, P, I, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, P, P, I,
+                                   P, L, P, L, L, I, P, STREAM]),
     # sampling.cu
     "fb_apply_penalties": (I, [P, L, I, P, P, P, P, P, P, I, STREAM]),
     "fb_apply_logit_bias": (I, [P, L, I, P, P, P, I, STREAM]),
     "fb_sample": (I, [P, L, I, I, P, P, P, P, P, P, STREAM]),
     # host side of the cache manager and of a step's descriptor (csrc/host_cache.cpp)
     "fbh_last_error": (c_char_p, []),
-    "fbh_cache_new": (P, [I, P, P, I, I, I]),
+    "fbh_cache_new": (P, [I, P, P, P, I, I, I]),
     "fbh_cache_free": (None, [P]),
     "fbh_has_slot": (I, [P]),
     "fbh_admit": (I, [P]),

@@ -212,11 +212,12 @@ def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, cos: torch.Tenso
 
 def rope_kv_write(q_in, q_out, k, v, cos, sin, half: int, positions, row_seq, block_table, k_pool, v_pool,
                   page_size: int, nh: int, nkv: int, hd: int, write_kv: bool, status, n_partials: int = 1,
-                  partial_stride: int = 0, table_base=None) -> None:
+                  partial_stride: int = 0, table_base=None, table_head: int = 0) -> None:
     """q_out = rotate(q_in) (q_out may be q_in); with write_kv, rotate k into the cache and copy v into it.
     q_in, k, v share one dtype (the projection's output); q_out and the cache share one dtype.  With
     n_partials > 1 the inputs are split-K shares `partial_stride` elements apart and are added first.
-    table_base (int32 per sequence, optional): the logical page that column 0 of each table row stands for."""
+    table_base (int32 per sequence, optional): the logical page that the first column behind the kept pages' of each
+    table row stands for; table_head: how many columns in front hold a request's kept first pages."""
     _cuda(q_in, q_out, k, v, cos, sin, positions, row_seq, block_table, k_pool, v_pool, status, table_base)
     _i32(table_base, "table_base")
     n = q_in.shape[0]
@@ -236,9 +237,9 @@ def rope_kv_write(q_in, q_out, k, v, cos, sin, half: int, positions, row_seq, bl
         _rows(k) if k is not None else 0,
         _ptr(v), _rows(v) if v is not None else 0, dtype_code(q_in), dtype_code(q_out), _ptr(cos), _ptr(sin), half,
         _ptr(positions), _ptr(row_seq), _ptr(block_table),
-        block_table.stride(0) if block_table is not None else 0, _ptr(table_base), _ptr(k_pool), _ptr(v_pool),
-        page_size, n_pages, n, nh, nkv if write_kv else 0, hd, 1 if write_kv else 0, status.data_ptr(), _stream()),
-        "rope_kv_write")
+        block_table.stride(0) if block_table is not None else 0, _ptr(table_base), int(table_head), _ptr(k_pool),
+        _ptr(v_pool), page_size, n_pages, n, nh, nkv if write_kv else 0, hd, 1 if write_kv else 0, status.data_ptr(),
+        _stream()), "rope_kv_write")
 
 
 ACTIVATIONS = {"silu": 1, "gelu_tanh": 2, "gelu_pytorch_tanh": 2}      # codes of the kernels' gate activations
@@ -375,7 +376,7 @@ def _slopes(score_slopes, nh: int) -> int:
 
 def paged_attention_simt(q, out, k_pool, v_pool, block_table, positions, row_seq, nh: int, nkv: int, hd: int,
                          window: int, scale: float, status, table_base=None, score_slopes=None, sinks=None,
-                         vd: int = 0, keep_first: int = 0) -> None:
+                         vd: int = 0, keep_first: int = 0, table_head: int = 0) -> None:
     """score_slopes (float32 per query head, optional): slope * (key position - query position) is added to every
     scaled score, a linear penalty on distance.  sinks (float32 per query head, optional): one more softmax slot per
     head whose score is that number, unscaled, and which has no value.  vd: the size of a value row where it is not
@@ -397,8 +398,8 @@ def paged_attention_simt(q, out, k_pool, v_pool, block_table, positions, row_seq
         raise KernelError("attention: cache pools must be contiguous")
     check(lib().fb_paged_attention_simt(
         q.data_ptr(), _rows(q), out.data_ptr(), _rows(out), dtype_code(q), k_pool.data_ptr(), v_pool.data_ptr(),
-        page_size, n_pages, block_table.data_ptr(), block_table.stride(0), _ptr(table_base), positions.data_ptr(),
-        row_seq.data_ptr(), n, nh, nkv, hd, vd, int(window), int(keep_first), float(scale), _slopes(score_slopes, nh),
+        page_size, n_pages, block_table.data_ptr(), block_table.stride(0), _ptr(table_base), int(table_head),
+        positions.data_ptr(), row_seq.data_ptr(), n, nh, nkv, hd, vd, int(window), int(keep_first), float(scale), _slopes(score_slopes, nh),
         _ptr(sinks), status.data_ptr(), _stream()), "paged_attention_simt")
 
 
@@ -736,7 +737,7 @@ def paged_attention_mma(q, out, k_pool, v_pool, block_table, seq_q_start, seq_q_
                         max_q_len: int, max_kv_len: int, any_short: bool, any_long: bool, nh: int, nkv: int,
                         hd: int, window: int, scale: float, status, table_base=None, prefetch=None,
                         multi_seqs=None, n_multi: int = 0, score_slopes=None, sinks=None,
-                        weights_float32: bool = False, keep_first: int = 0) -> None:
+                        weights_float32: bool = False, keep_first: int = 0, table_head: int = 0) -> None:
     """bfloat16 attention on the tensor cores over the paged cache; sequences are described per entry of the
     step (first row, rows, first position).  any_short / any_long say whether the step holds sequences with
     rows * (nh/nkv) <= 16 / > 16 (attention_is_short), which run in different arrangements of the kernel.  table_base (int32 per
@@ -767,7 +768,7 @@ def paged_attention_mma(q, out, k_pool, v_pool, block_table, seq_q_start, seq_q_
     scratch = _AttentionScratch.get(q.device, n_seqs, nkv * attention_kv_share(nh, nkv), hd)
     check(lib().fb_paged_attention_mma(
         q.data_ptr(), _rows(q), out.data_ptr(), _rows(out), k_pool.data_ptr(), v_pool.data_ptr(), page_size, n_pages,
-        block_table.data_ptr(), block_table.stride(0), _ptr(table_base), seq_q_start.data_ptr(),
+        block_table.data_ptr(), block_table.stride(0), _ptr(table_base), int(table_head), seq_q_start.data_ptr(),
         seq_q_len.data_ptr(), seq_pos_start.data_ptr(), _ptr(multi_seqs), int(n_multi), n_seqs, max_q_len, max_kv_len,
         1 if any_short else 0,
         1 if any_long else 0, nh, nkv, hd, int(window), int(keep_first), float(scale), _slopes(score_slopes, nh), _ptr(sinks),
@@ -805,11 +806,12 @@ def paged_attention(ctx, q, out, cache, nh: int, nkv: int, hd: int, window: int,
                             nh, nkv, hd, window, scale, ctx.runtime.status, table_base=cache.table_base,
                             prefetch=next_weight, multi_seqs=b.multi_seqs_d, n_multi=b.n_multi,
                             score_slopes=score_slopes, sinks=sinks, weights_float32=weights_float32,
-                            keep_first=keep_first)
+                            keep_first=keep_first, table_head=cache.table_head)
     else:
         paged_attention_simt(q, out, cache.k_pool, cache.v_pool, cache.block_table, b.positions, b.row_seq,
                              nh, nkv, hd, window, scale, ctx.runtime.status, table_base=cache.table_base,
-                             score_slopes=score_slopes, sinks=sinks, vd=vd, keep_first=keep_first)
+                             score_slopes=score_slopes, sinks=sinks, vd=vd, keep_first=keep_first,
+                             table_head=cache.table_head)
 
 
 def diff_attention_mma_supported(q: torch.Tensor, nh: int, nkv: int, kd: int, vd: int) -> bool:
@@ -918,7 +920,7 @@ def qk_norm_rope_kv_write(proj: torch.Tensor, q_weight, k_weight, reach, eps: fl
         dtype_code(q_weight) if q_weight is not None else 0, code, float(eps), float(weight_offset), _ptr(cos),
         _ptr(sin), int(half), q_out.data_ptr(), _rows(q_out), dtype_code(q_out), positions.data_ptr(),
         row_seq.data_ptr(), cache.block_table.data_ptr(), cache.block_table.stride(0), _ptr(cache.table_base),
-        k_pool.data_ptr(), v_pool.data_ptr(), cache.page_size, n_pages, n, nh, nkv, hd, vd,
+        int(cache.table_head), k_pool.data_ptr(), v_pool.data_ptr(), cache.page_size, n_pages, n, nh, nkv, hd, vd,
         1 if cache.writable else 0, status.data_ptr(), _stream()), "qk_norm_rope_kv_write")
 
 

@@ -168,8 +168,7 @@ def measure(name: str, size: dict, layers: int, batch: int, context: int, prefil
     out = {"size": dict(size), "layers": layers, "batch": batch, "context": context, "prefill_tokens": prefill}
     for design, cfg in configs(size, layers).items():
         say(f"{name}: building {design}, {layers} layers")
-        # Tubepel keeps every page until a request ends (the latents have no window, the windowed groups keep their
-        # first keys); Fegizen gives back what its window has passed
+        # Tubepel's latents have no window: every page of a request stays until it ends
         live = context if design == "tubepel" else min(context, size["window"] + PAGE)
         per_seq = -(-(live + 2 * PAGE + steps + warmup + 64) // PAGE) * PAGE
         engine = Engine.from_config(cfg, seed=0, options=EngineOptions(

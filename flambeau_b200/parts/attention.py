@@ -42,7 +42,8 @@ class PagedAttention(Mixer):
     designs that say their attention weights are 32-bit numbers; otherwise they are rounded to bfloat16 for that
     product, as flash attention kernels do.
     `keep_first` (with a window): the keys at positions below this stay visible to every later query, at their true
-    positions (for rotation and distances); a request's pages are then kept until it ends.
+    positions (for rotation and distances); the pages that hold them are kept while the request lives, whatever the
+    window gives back behind them.
     `gate` (bool): the heads' outputs are multiplied element by element by sigmoid(Wg h) before the output projection
     (`<prefix><names.g>`, [num_heads * value_dim, width]; Wg reads the same input as the other projections and is
     part of their one product).
@@ -219,12 +220,13 @@ class PagedAttention(Mixer):
                 ops.rope_kv_write(q_in, q, k, v, cos, sin, half, b.positions, b.row_seq, cache.block_table,
                                   cache.k_pool, cache.v_pool, cache.page_size, self.nh, self.nkv, self.hd,
                                   cache.writable, rt.status, n_partials=parts, partial_stride=stride,
-                                  table_base=cache.table_base)
+                                  table_base=cache.table_base, table_head=cache.table_head)
             else:
                 pos.rotate(ctx, q_in, k if cache.writable else None)
                 ops.rope_kv_write(q_in, q, k, v, None, None, 0, b.positions, b.row_seq, cache.block_table,
                                   cache.k_pool, cache.v_pool, cache.page_size, self.nh, self.nkv, self.hd,
-                                  cache.writable, rt.status, table_base=cache.table_base)
+                                  cache.writable, rt.status, table_base=cache.table_base,
+                                  table_head=cache.table_head)
             a = ctx.ws.alloc((n, self.qw), rt.dtype)
             # few rows: the attention kernel fetches the start of the output projection's weights into L2 at its end
             hint = self.o.weight if ctx.l2_hints and n <= 64 else None

@@ -55,10 +55,12 @@ class KVRequirement:
 
     @property
     def release_window(self) -> int:
-        """The window by which the cache manager gives pages back (0: never before the request ends).  A group whose
-        first keys stay visible keeps all its pages: a table row is one run of consecutive logical pages, and the
-        kept pages and the window's would be two."""
-        return 0 if self.keep_first > 0 else self.window
+        """The window by which the cache manager gives pages back (0: never before the request ends)."""
+        return self.window
+
+    def kept_pages(self, page_size: int) -> int:
+        """Pages at a request's start that a window never gives back: those that hold its kept first keys."""
+        return -(-self.keep_first // page_size) if self.window > 0 and self.keep_first > 0 else 0
 
 
 @dataclass(frozen=True)

@@ -278,3 +278,105 @@ def test_snapshot_and_restore_bring_a_request_back(window):
         cm.restore("c", big)
     assert cm.free_pages() == [0] and "c" not in cm.requests
     cm.check_invariants()
+
+
+@pytest.mark.parametrize("keep_first", [1, 8, 9, 30])
+def test_a_window_gives_back_all_but_the_pages_of_the_kept_first_keys(keep_first):
+    """Under a window that keeps a request's first keys visible, the pages that hold those keys stay while the request
+    lives; everything between them and the window goes back as it dies.  A table row is the kept pages, then the live
+    ones, and a request runs on far past what the row could address from position 0."""
+    page, window = 8, 24
+    kept = -(-keep_first // page)
+    req = KVRequirement(1, 8, window, keep_first=keep_first)
+    assert req.kept_pages(page) == kept and KVRequirement(1, 8, 0, keep_first=keep_first).kept_pages(page) == 0
+    cm = CacheManager([CallPlan(kv=req)], max_tokens=160, page_size=page, max_requests=2, device="cpu",
+                      dtype=torch.float32, max_seq_len=100000, max_step_tokens=16)
+    assert cm.table_pages == -(-(window + 16) // page) + 2 + kept
+    cm.admit("a")
+    for _ in range(200):
+        cm.reserve("a", 16)
+        live = [p for p in cm.requests["a"].pages[0] if p >= 0]
+        assert len(live) <= cm.table_pages
+        cm.commit("a", 16)
+        cm.check_invariants()
+    length = cm.length("a")
+    first_live = length - window + 1
+    pages = list(cm.requests["a"].pages[0])
+    for j, p in enumerate(pages):
+        assert (p < 0) == (j >= kept and (j + 1) * page <= first_live), j
+    assert cm.first_live_page("a", 0) == first_live // page
+    held = sum(1 for p in pages if p >= 0)
+    assert held == kept + len(pages) - first_live // page
+    assert cm.free_pages() == [20 - held]
+    # a second request takes what the first gave back, and both leave everything behind
+    cm.admit("b")
+    cm.reserve("b", 5)
+    cm.commit("b", 5)
+    assert list(cm.requests["b"].pages[0]) and cm.first_live_page("b", 0) == kept, "nothing given back yet"
+    cm.release("a")
+    cm.release("b")
+    assert cm.free_pages() == [20]
+
+
+def test_the_step_descriptor_lists_kept_pages_in_front_of_the_live_ones():
+    from flambeau_b200.engine.batch import BatchBuffers, Entry
+    page = 4
+    plans = [CallPlan(kv=KVRequirement(1, 8, 6, keep_first=5)), CallPlan(kv=KVRequirement(1, 8, 6))]
+    cm = CacheManager(plans, max_tokens=64, page_size=page, max_requests=2, device="cpu", dtype=torch.float32,
+                      max_seq_len=1000, max_step_tokens=8)
+    buffers = BatchBuffers(torch.device("cpu"), 8, 2, cm.n_groups, cm.table_pages)
+    cm.admit("a")
+    cm.reserve("a", 3)
+    batch = buffers.build([Entry("a", [1, 2, 3], [])], cm, 100)
+    kept_group = cm.group_of_call[0]
+    row = buffers.h_tables[kept_group, 0].tolist()
+    logical = list(cm.requests["a"].pages[kept_group])
+    assert row[:2] == [logical[0], -1] and all(p == -1 for p in row[2:]), "two columns for the kept pages, one filled"
+    cm.commit("a", 3)
+    for _ in range(6):
+        cm.reserve("a", 5)
+        cm.commit("a", 5)                                         # 33 tokens: the window has passed pages 2 to 5
+    cm.reserve("a", 2)
+    batch = buffers.build([Entry("a", [1, 2], [1])], cm, 100)
+    logical = list(cm.requests["a"].pages[kept_group])
+    base = cm.first_live_page("a", kept_group)
+    assert base == (33 - 6 + 1) // page and logical[2:base] == [-1] * (base - 2)
+    row = buffers.h_tables[kept_group, 0].tolist()
+    assert row[:2] == logical[:2] and row[2:2 + len(logical) - base] == logical[base:]
+    assert int(buffers.h_seqs[4 + kept_group, 0]) == base
+    other = cm.group_of_call[1]
+    assert buffers.h_tables[other, 0].tolist()[:len(logical) - base] == list(cm.requests["a"].pages[other])[base:]
+    assert batch.n_tokens == 2
+
+
+def test_snapshot_and_restore_keep_the_kept_pages():
+    plans = [CallPlan(kv=KVRequirement(2, 4, 24, keep_first=10))]
+    cm = CacheManager(plans, max_tokens=160, page_size=8, max_requests=4, device="cpu", dtype=torch.float32,
+                      max_seq_len=512)
+    g = cm.groups[0]
+    for t in list(g.k.values()) + list(g.v.values()):
+        t.copy_(torch.arange(t.numel(), dtype=torch.float32).view_as(t))
+    cm.admit("a")
+    for _ in range(11):
+        cm.reserve("a", 7)
+        cm.commit("a", 7)                                                      # 77 tokens
+    before = list(cm.requests["a"].pages[0])
+    live = [p for p in before if p >= 0]
+    assert [p >= 0 for p in before[:2]] == [True, True] and before[2] == -1
+    snap = cm.snapshot("a")
+    assert snap.k[0].shape[0] == len(live) and torch.equal(snap.k[0], g.k[0][live])
+    cm.release("a")
+    cm.admit("other")
+    cm.reserve("other", 30)
+    cm.commit("other", 30)
+    cm.restore("b", snap)
+    cm.check_invariants()
+    after = list(cm.requests["b"].pages[0])
+    assert [p < 0 for p in after] == [p < 0 for p in before] and cm.length("b") == 77
+    now_live = [p for p in after if p >= 0]
+    assert torch.equal(g.k[0][now_live], snap.k[0]) and torch.equal(g.v[0][now_live], snap.v[0])
+    cm.reserve("b", 40)
+    cm.commit("b", 40)
+    assert all(p >= 0 for p in list(cm.requests["b"].pages[0])[:2]), "the kept pages are still there"
+    cm.release_all()
+    assert cm.free_pages() == [20]

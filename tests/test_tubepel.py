@@ -70,8 +70,9 @@ def test_run_order_and_caches():
     assert len(plans) == 8 and all(p.state is None for p in plans)
     kv = plans[0].kv
     assert (kv.kv_heads, kv.head_dim, kv.value_dim, kv.window, kv.keep_first) == (2, 16, 24, 9, 2)
-    assert kv.release_window == 0, "pages of a group whose first keys stay visible are kept until the request ends"
-    assert plans[7].kv.release_window == 20 and plans[7].kv.keep_first == 0
+    assert kv.release_window == 9 and kv.kept_pages(16) == 1 and kv.kept_pages(1) == 2, \
+        "the window gives pages back; those that hold the kept first keys stay"
+    assert plans[7].kv.release_window == 20 and plans[7].kv.keep_first == 0 and plans[7].kv.kept_pages(16) == 0
     lat = plans[1].kv
     assert (lat.kv_heads, lat.head_dim, lat.window, lat.values_in_keys) == (1, 48, 0, True)
     assert plans[1].kv == plans[3].kv == plans[5].kv and plans[2].kv.head_dim == 32

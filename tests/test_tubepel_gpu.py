@@ -81,12 +81,17 @@ def test_output_gate(shape, dtype):
     assert rel_err(a_d, want) < (1e-6 if dtype == "float32" else 5e-3)
 
 
-def paged_keys_and_values(seqs, ks, vs, *, page_size, dtype, seed=0):
+def paged_keys_and_values(seqs, ks, vs, *, page_size, dtype, seed=0, window=0, keep=0, given_back=False):
     """Keys [tokens, kv heads, d] and values [tokens, kv heads, e] of some sequences scattered over pages handed out
-    in random order; slots never written hold NaN.  `seqs`: (tokens before the step, tokens of the step)."""
+    in random order; slots never written hold NaN.  `seqs`: (tokens before the step, tokens of the step).
+    `given_back`: the cache has given back what the window had passed before the step, but for the pages of the kept
+    first keys: those pages do not exist (whatever reads them reads NaN), and a table row is the kept pages' columns,
+    then the pages from the first live one on."""
     from flambeau_b200.cache.manager import LayerCacheView
     g = torch.Generator().manual_seed(seed)
     G, d, e = ks[0].shape[1], ks[0].shape[2], vs[0].shape[2]
+    kept = -(-keep // page_size) if given_back and window and keep else 0
+    first = [max(kept, max(0, ctx - window + 1) // page_size) if given_back and window else kept for ctx, _ in seqs]
     count = [-(-(ctx + n) // page_size) for ctx, n in seqs]
     total = sum(count) + 3
     order = torch.randperm(total, generator=g).tolist()
@@ -95,12 +100,14 @@ def paged_keys_and_values(seqs, ks, vs, *, page_size, dtype, seed=0):
     v_pool = torch.full((total, G, page_size, e), float("nan"), dtype=dtype)
     for s, (ctx, n) in enumerate(seqs):
         for j in range(count[s]):
+            if kept <= j < first[s]:
+                continue                                    # given back
             page = order.pop()
-            table[s, j] = page
+            table[s, j if j < kept else j - first[s] + kept] = page
             lo, hi = j * page_size, min((j + 1) * page_size, ctx + n)
             k_pool[page, :, :hi - lo] = ks[s][lo:hi].transpose(0, 1).to(dtype)
             v_pool[page, :, :hi - lo] = vs[s][lo:hi].transpose(0, 1).to(dtype)
-    return LayerCacheView(k_pool.to(DEV), v_pool.to(DEV), table.to(DEV), i32([0] * len(seqs)), page_size, False, 0, None)
+    return LayerCacheView(k_pool.to(DEV), v_pool.to(DEV), table.to(DEV), i32(first), page_size, False, 0, None, kept)
 
 
 KEPT_GEOMETRIES = [(4, 2, 64, 64, 136, 4, 16), (4, 2, 16, 24, 9, 2, 16), (6, 1, 64, 64, 70, 66, 16), (2, 2, 128, 128, 40, 130, 32),
@@ -110,13 +117,16 @@ KEPT_GEOMETRIES = [(4, 2, 64, 64, 136, 4, 16), (4, 2, 16, 24, 9, 2, 16), (6, 1, 
 
 @pytest.mark.parametrize("geometry", KEPT_GEOMETRIES, ids=lambda g: "h%d-g%d-d%d-e%d-w%d-f%d-p%d" % g)
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_attention_under_a_window_that_keeps_the_first_keys(geometry, dtype):
+@pytest.mark.parametrize("given_back", [False, True], ids=["all-pages", "dead-pages-given-back"])
+def test_attention_under_a_window_that_keeps_the_first_keys(geometry, dtype, given_back):
     """Grouped heads over the paged cache with a sink in every head.  Sequences that are first tokens, positions just
     behind the window's length (where the kept keys first part from the window), decoded tokens far into a request and
     at page borders, portions starting in mid-page and portions of two tokens.  For the first and the last query of
     each, four keys are made to stand out along the query of head 0: the key at the window's far edge (seen), the one
     just outside it (stronger, not seen), the last kept key (seen) and the first key that is not kept (strongest, not
-    seen unless the window reaches it): a mask that is one key off anywhere takes the softmax over."""
+    seen unless the window reaches it): a mask that is one key off anywhere takes the softmax over.  Once with every
+    page in the table, once with the pages between the kept keys and the window given back (reading one is reading
+    NaN)."""
     from flambeau_b200.kernels import ops
     nh, nkv, d, e, window, keep, page = geometry
     dt = DT[dtype]
@@ -141,7 +151,7 @@ def test_attention_under_a_window_that_keeps_the_first_keys(geometry, dtype):
         ks.append(k)
         vs.append(v)
     sinks = torch.randn(nh, generator=g)
-    cache = paged_keys_and_values(seqs, ks, vs, page_size=page, dtype=dt)
+    cache = paged_keys_and_values(seqs, ks, vs, page_size=page, dtype=dt, window=window, keep=keep, given_back=given_back)
     want = []
     for (ctx, n), q, k, v in zip(seqs, qs, ks, vs):
         seen = pt.visible(ctx + n, window, keep)[ctx:]
