@@ -51,7 +51,7 @@ struct AttnArgs {
                                           // the arrangements for portions covers only these (nullptr: all n_seqs)
     int nh, nkv, hd, window;
     int keep_first;                    // under a window: the first keys of a sequence (positions below this) stay
-                                       // visible to every later query, at their true positions; 0: none
+                                       // visible to every later query, each where it was written; 0: none
     float scale_log2e;
     const float* score_slopes;         // per query head, or nullptr: slope * (key position - query position) is added
                                        // to the scaled score (a linear penalty on distance; <= 0 for the keys a

@@ -41,9 +41,9 @@ class PagedAttention(Mixer):
     in bfloat16 (two bfloat16 numbers a weight, two MMAs for one; the 32-bit mode has them in float32 anyway), for
     designs that say their attention weights are 32-bit numbers; otherwise they are rounded to bfloat16 for that
     product, as flash attention kernels do.
-    `keep_first` (with a window): the keys at positions below this stay visible to every later query, at their true
-    positions (for rotation and distances); the pages that hold them are kept while the request lives, whatever the
-    window gives back behind them.
+    `keep_first` (with a window): the keys at positions below this stay visible to every later query, each with the
+    position it was written at (which its rotation and the window's distances use); the pages that hold them are kept
+    while the request lives, whatever the window gives back behind them.
     `gate` (bool): the heads' outputs are multiplied element by element by sigmoid(Wg h) before the output projection
     (`<prefix><names.g>`, [num_heads * value_dim, width]; Wg reads the same input as the other projections and is
     part of their one product).

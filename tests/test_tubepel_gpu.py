@@ -110,7 +110,7 @@ def paged_keys_and_values(seqs, ks, vs, *, page_size, dtype, seed=0, window=0, k
     return LayerCacheView(k_pool.to(DEV), v_pool.to(DEV), table.to(DEV), i32(first), page_size, False, 0, None, kept)
 
 
-KEPT_GEOMETRIES = [(4, 2, 64, 64, 136, 4, 16), (4, 2, 16, 24, 9, 2, 16), (6, 1, 64, 64, 70, 66, 16), (2, 2, 128, 128, 40, 130, 32),
+KEPT_GEOMETRIES = [(8, 2, 64, 64, 120, 3, 16), (4, 2, 16, 24, 9, 2, 16), (6, 1, 64, 64, 70, 66, 16), (2, 2, 128, 128, 40, 130, 32),
                    (8, 4, 32, 32, 33, 17, 8), (3, 3, 24, 8, 20, 1, 16), (2, 1, 8, 8, 1, 1, 16), (4, 4, 64, 64, 100, 64, 64),
                    (2, 1, 40, 40, 30, 0, 16), (20, 1, 64, 64, 50, 5, 16)]
 
